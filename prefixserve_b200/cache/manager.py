@@ -18,7 +18,7 @@ The reference keeps this split between a C++ pool/tree and Python lists on the
 request (csrc/block_manager.hpp, csrc/radix_tree.hpp,
 prefixserve/scheduler.py:370-451, prefixserve/llama_engine.py:110-117); here
 one object owns ids, tables, slots and the device tensors.
-Cache layout of an entry: [num_pages, 2 (key, value), kv_heads, page_size, head_dim].
+Cache layout of an entry: [num_pages, planes (key, value; or one shared row), kv_heads, page_size, head_dim].
 
 What a step needs to know about a request stays on the device in one int32
 array (``resident``): a record per slot (position, sampling temperature and
@@ -136,7 +136,7 @@ class CacheManager:
             for i, need in enumerate(self.needs):
                 if need.paged is not None:
                     g = self.groups[self.entry_group[i]]
-                    shape = (g.pool.num_blocks, 2, need.paged.num_kv_heads, page_size, need.paged.head_dim)
+                    shape = (g.pool.num_blocks, need.paged.planes, need.paged.num_kv_heads, page_size, need.paged.head_dim)
                     self.kv[i] = self._pages(shape, dtype)
                 if need.state is not None:
                     self.state[i] = torch.zeros((num_slots, *need.state.shape), dtype=need.state.dtype, device=self.device)
@@ -176,7 +176,7 @@ class CacheManager:
         out: dict[int | None, int] = {}
         for n in needs:
             if n.paged is not None:
-                out[n.paged.window] = out.get(n.paged.window, 0) + 2 * n.paged.num_kv_heads * page_size * n.paged.head_dim * item
+                out[n.paged.window] = out.get(n.paged.window, 0) + n.paged.planes * n.paged.num_kv_heads * page_size * n.paged.head_dim * item
         return out
 
     def num_pages(self, group: int = 0) -> int:

@@ -1,4 +1,5 @@
 from .llama import Llama3RopeScaling, LlamaConfig, UnsupportedModelError
+from .nerenex import LatentAttentionConfig, NerenexConfig, NerenexLayer, RecurrentConfig
 from .registry import (
     Architecture,
     UnknownArchitectureError,
@@ -11,7 +12,8 @@ from .registry import (
 from .spec import LayerCall, LayerSpec, ModelSpec, PartSpec, part, sequential_schedule
 
 __all__ = [
-    "Architecture", "LayerCall", "LayerSpec", "Llama3RopeScaling", "LlamaConfig", "ModelSpec", "PartSpec",
+    "Architecture", "LatentAttentionConfig", "LayerCall", "LayerSpec", "Llama3RopeScaling", "LlamaConfig", "ModelSpec",
+    "NerenexConfig", "NerenexLayer", "PartSpec", "RecurrentConfig",
     "UnknownArchitectureError", "UnsupportedModelError", "architecture_of", "get_architecture", "part",
     "read_model_folder", "register_architecture", "registered_architectures", "sequential_schedule",
 ]

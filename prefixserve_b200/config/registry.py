@@ -59,6 +59,8 @@ def get_architecture(name: str) -> Architecture:
 def architecture_of(raw: Mapping[str, Any]) -> Architecture:
     """Picks the record from a parsed config.json."""
     names = raw.get("architectures") or []
+    if not names and isinstance(raw.get("architecture"), str):  # some designs give one name instead of a list
+        names = [raw["architecture"]]
     if names:
         return get_architecture(str(names[0]))
     # Hand-written folders sometimes give only model_type.

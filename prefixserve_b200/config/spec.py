@@ -47,7 +47,7 @@ def part(kind: str, **params: Any) -> PartSpec:
 @dataclass(frozen=True)
 class LayerSpec:
     """One block: a mixer, a feed-forward and their norms, put together by the named arrangement
-    (``parts.block``: "pre_norm", "parallel", or one registered there).  ``ffn`` and ``ffn_norm`` may be None: a
+    (``parts.block``: "pre_norm", "parallel", "gated_post_norm", or one registered there).  ``ffn`` and ``ffn_norm`` may be None: a
     layer that only mixes."""
 
     mixer: PartSpec
@@ -55,6 +55,12 @@ class LayerSpec:
     mixer_norm: PartSpec
     ffn_norm: PartSpec | None
     arrangement: str = "pre_norm"
+    # For arrangements that gate a sublayer's result by a function of its input before it joins the stream
+    # ("gated_post_norm"): the gate of the mixer's and of the feed-forward's result (None: no gate), and the factor
+    # the normed result is multiplied by when it is added.
+    mixer_gate: PartSpec | None = None
+    ffn_gate: PartSpec | None = None
+    residual_scale: float = 1.0
 
     def __post_init__(self) -> None:
         if (self.ffn is None) != (self.ffn_norm is None):

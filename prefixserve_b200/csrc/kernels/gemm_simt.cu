@@ -20,11 +20,15 @@ constexpr int THREADS = 256;  // 16 x 16 threads, 4 x 4 outputs each
 template <typename TA, typename TW, typename TC>
 __global__ void __launch_bounds__(THREADS)
 gemm_nt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TC* __restrict__ C, int M, int N, int K,
-               int64_t lda, int64_t ldw, int64_t ldc, int accumulate) {
+               int64_t lda, int64_t ldw, int64_t ldc, int accumulate, int64_t batch_a, int64_t batch_w, int64_t batch_c) {
   __shared__ float sa[BK][TILE + 4];
   __shared__ float sw[BK][TILE + 4];
   pdl_trigger();
   pdl_wait();
+  // blockIdx.z: one of several products of the same shape whose operands lie a fixed stride apart (one per head or block)
+  A += (size_t)blockIdx.z * batch_a;
+  W += (size_t)blockIdx.z * batch_w;
+  C += (size_t)blockIdx.z * batch_c;
   const int m0 = blockIdx.y * TILE, n0 = blockIdx.x * TILE;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   float acc[4][4] = {};
@@ -72,11 +76,12 @@ gemm_nt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TC* __restric
 
 template <typename TA, typename TW>
 int launch_c(const void* a, const void* w, void* c, int c_dtype, int M, int N, int K, int64_t lda, int64_t ldw,
-             int64_t ldc, int accumulate, cudaStream_t stream) {
-  dim3 grid((N + TILE - 1) / TILE, (M + TILE - 1) / TILE);
+             int64_t ldc, int accumulate, cudaStream_t stream, int batch = 1, int64_t batch_a = 0, int64_t batch_w = 0,
+             int64_t batch_c = 0) {
+  dim3 grid((N + TILE - 1) / TILE, (M + TILE - 1) / TILE, batch);
   if (grid.y > 65535) PSB_REFUSE("gemm_nt: M=%d is too large for this kernel", M);
   PSB_DISPATCH_DTYPE(c_dtype, TC, {
-    psb_launch(gemm_nt_kernel<TA, TW, TC>, grid, dim3(THREADS), 0, stream, (const TA*)a, (const TW*)w, (TC*)c, M, N, K, lda, ldw, ldc, accumulate);
+    psb_launch(gemm_nt_kernel<TA, TW, TC>, grid, dim3(THREADS), 0, stream, (const TA*)a, (const TW*)w, (TC*)c, M, N, K, lda, ldw, ldc, accumulate, batch_a, batch_w, batch_c);
   });
   return 0;
 }
@@ -96,5 +101,25 @@ PSB_API int psb_gemm_nt(const void* a, int a_dtype, const void* w, int w_dtype, 
   });
   if (rc) return rc;
   PSB_LAUNCH_CHECK("gemm_nt");
+  return 0;
+}
+
+// ``batch`` products of one shape in one launch: product b reads A + b*batch_a and W + b*batch_w and writes
+// C + b*batch_c (strides in elements).  For per-head and block-diagonal matrices: the heads' operands are slices of
+// one [tokens, heads * size] tensor, so the leading dimensions stay those of the whole tensor.
+PSB_API int psb_gemm_nt_batched(const void* a, int a_dtype, const void* w, int w_dtype, void* c, int c_dtype, int M, int N,
+                                int K, int64_t lda, int64_t ldw, int64_t ldc, int batch, int64_t batch_a, int64_t batch_w,
+                                int64_t batch_c, cudaStream_t stream) {
+  if (M < 0 || N < 1 || K < 1 || batch < 1 || batch > 65535) PSB_REFUSE("gemm_nt_batched: bad sizes M=%d N=%d K=%d batch=%d", M, N, K, batch);
+  if (lda < K || ldw < K || ldc < N) PSB_REFUSE("gemm_nt_batched: a leading dimension is smaller than its row");
+  if (M == 0) return 0;
+  int rc = 0;
+  PSB_DISPATCH_DTYPE(a_dtype, TA, {
+    PSB_DISPATCH_DTYPE(w_dtype, TW, {
+      rc = launch_c<TA, TW>(a, w, c, c_dtype, M, N, K, lda, ldw, ldc, 0, stream, batch, batch_a, batch_w, batch_c);
+    });
+  });
+  if (rc) return rc;
+  PSB_LAUNCH_CHECK("gemm_nt_batched");
   return 0;
 }

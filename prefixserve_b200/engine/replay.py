@@ -72,9 +72,10 @@ class Replayer:
         self.dtype = parse_dtype(dtype)
         self.device = torch.device(device)
         self.max_live = max_live
-        _, _, self.model = load_model(model_dir, dtype=self.dtype, device=self.device)
-        spec = self.model.spec
         pages = max(1, pages_for(max_tokens, page_size))
+        # start-up tables (rotary angles) only as far as the pool lets a request grow
+        _, _, self.model = load_model(model_dir, dtype=self.dtype, device=self.device, max_positions=pages * page_size)
+        spec = self.model.spec
         max_seq_len = min(spec.max_positions, pages * page_size)
         self.cache = CacheManager(self.model.cache_needs(), num_pages=pages, num_slots=max_live,
                                   max_seq_len=max_seq_len, page_size=page_size, dtype=self.dtype, device=self.device,

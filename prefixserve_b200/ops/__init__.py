@@ -7,6 +7,16 @@ from .kernels import (  # noqa: F401
     ACTIVATIONS,
     KernelError,
     act_mul,
+    activation,
+    causal_conv,
+    gated_norm_add,
+    hashed_embedding,
+    latent_attention,
+    latent_prepare,
+    latent_query_rotate,
+    linear_per_head,
+    recurrence_scan,
+    UNARY_ACTIVATIONS,
     add_rmsnorm,
     attention,
     embedding,

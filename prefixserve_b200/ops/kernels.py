@@ -404,3 +404,202 @@ def step_prepare(records: torch.Tensor | None, kv_len: torch.Tensor | None, slot
         return
     check(lib().psb_step_prepare(_ptr(records), record_words, _ptr(kv_len), slots.data_ptr(), _ptr(rows), row_width, _ptr(out),
                                  width, b, num_slots, _stream()), "step_prepare")
+
+
+def linear_per_head(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,
+                    out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """out[t, h, :] = w[h] @ a[t, h, :] for a [T, heads, K] (a view whose last axis is contiguous and whose head axis
+    has a fixed stride: a slice of a wider [T, heads, more] tensor will do), w [heads, N, K] contiguous, out
+    [T, heads, N] (again possibly a slice of a wider tensor).  Per-head and block-diagonal matrices; float32 sums."""
+    _dev(w, "per-head weight")
+    if a.dim() != 3 or w.dim() != 3 or a.shape[1] != w.shape[0] or a.shape[2] != w.shape[2] or a.stride(2) != 1 or not a.is_cuda:
+        raise KernelError(f"cannot multiply rows {tuple(a.shape)} (strides {a.stride()}) by per-head matrices {tuple(w.shape)}")
+    t, heads, k = a.shape
+    n = w.shape[1]
+    if out is None:
+        out = torch.empty((t, heads, n), dtype=out_dtype or a.dtype, device=a.device)
+    if tuple(out.shape) != (t, heads, n) or out.stride(2) != 1 or not out.is_cuda:
+        raise KernelError(f"per-head product output must be [{t}, {heads}, {n}] with a contiguous last axis")
+    check(lib().psb_gemm_nt_batched(a.data_ptr(), _code(a, "left operand"), w.data_ptr(), _code(w, "weight"), out.data_ptr(),
+                                    _code(out, "product"), t, n, k, a.stride(0), k, out.stride(0), heads, a.stride(1),
+                                    n * k, out.stride(1), _stream()), "gemm_nt_batched")
+    return out
+
+
+def hashed_embedding(ids: torch.Tensor, positions: torch.Tensor, token_item: torch.Tensor, item_start: torch.Tensor,
+                     slots: torch.Tensor, last_token: torch.Tensor, table: torch.Tensor, pair_table: torch.Tensor, *,
+                     mul_prev: int, mul_cur: int, copy_dtype: torch.dtype | None = None):
+    """h[t] = float32(table[ids[t]]) + float32(pair_table[(prev * mul_prev + ids[t] * mul_cur) mod buckets]), the last
+    row of pair_table at position 0; ``prev`` of a portion's first token comes from ``last_token`` [num_slots], which is
+    then set to the portion's last token.  Returns (h float32, a copy in ``copy_dtype`` or None)."""
+    for what, x in (("token ids", ids), ("positions", positions), ("token-to-item map", token_item), ("item offsets", item_start),
+                    ("slots", slots), ("last tokens", last_token)):
+        _i32(x, what)
+    _dev(table, "embedding table"), _dev(pair_table, "pair table")
+    t, (v, h) = ids.numel(), table.shape
+    if pair_table.dim() != 2 or pair_table.shape[1] != h or pair_table.shape[0] < 2 or pair_table.dtype != table.dtype:
+        raise KernelError(f"pair table {tuple(pair_table.shape)} {pair_table.dtype} does not fit the embedding table {tuple(table.shape)} {table.dtype}")
+    out = torch.empty((t, h), dtype=torch.float32, device=ids.device)
+    copy = torch.empty((t, h), dtype=copy_dtype, device=ids.device) if copy_dtype not in (None, torch.float32) else None
+    check(lib().psb_hashed_embedding(ids.data_ptr(), positions.data_ptr(), token_item.data_ptr(), item_start.data_ptr(),
+                                     slots.data_ptr(), last_token.data_ptr(), table.data_ptr(), pair_table.data_ptr(),
+                                     _code(table, "embedding table"), out.data_ptr(), _ptr(copy),
+                                     _code(copy, "copy") if copy is not None else F32, t, slots.numel(), h, v,
+                                     pair_table.shape[0] - 1, int(mul_prev), int(mul_cur), last_token.numel(), _stream()),
+          "hashed_embedding")
+    return out, copy
+
+
+def gated_norm_add(h: torch.Tensor, y: torch.Tensor, gate: torch.Tensor | None, gate_bias: torch.Tensor | None,
+                   gain: torch.Tensor, eps: float, mult: float, copy_dtype: torch.dtype | None = None) -> torch.Tensor | None:
+    """h += mult * gain * rmsnorm(y * sigmoid(gate + gate_bias)) in place (h float32; without ``gate`` the norm is taken
+    of y itself).  Returns the new h in ``copy_dtype`` (None when that is float32 or not asked for: read h)."""
+    if isinstance(y, PendingProduct):
+        y = y.tensor()
+    _dev(h, "residual stream"), _dev(y, "sublayer output"), _dev(gain, "norm gain")
+    if h.dtype != torch.float32 or h.dim() != 2 or y.shape != h.shape:
+        raise KernelError(f"residual stream must be float32 [T, H] and the output must match it: {h.dtype} {tuple(h.shape)} vs {tuple(y.shape)}")
+    rows, width = h.shape
+    if gain.dtype != torch.float32 or gain.numel() != width:
+        raise KernelError(f"norm gain must be float32 [{width}]")
+    if gate is not None:
+        _dev(gate, "gate")
+        if gate.shape != h.shape:
+            raise KernelError(f"gate {tuple(gate.shape)} does not match the stream {tuple(h.shape)}")
+        if gate_bias is not None and (gate_bias.dtype != torch.float32 or gate_bias.numel() != width or not gate_bias.is_cuda):
+            raise KernelError(f"gate bias must be float32 [{width}] on the device")
+    copy = torch.empty((rows, width), dtype=copy_dtype, device=h.device) if copy_dtype not in (None, torch.float32) else None
+    check(lib().psb_gated_norm_add(h.data_ptr(), y.data_ptr(), _code(y, "sublayer output"), _ptr(gate),
+                                   _code(gate, "gate") if gate is not None else F32, _ptr(gate_bias) if gate is not None else None,
+                                   gain.data_ptr(), _ptr(copy), _code(copy, "copy") if copy is not None else F32, rows, width,
+                                   float(eps), float(mult), _stream()), "gated_norm_add")
+    return copy
+
+
+UNARY_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "xielu": 2}  # the codes of activation.cu; xielu takes two learned numbers
+
+
+def activation(x: torch.Tensor, name: str, params: torch.Tensor | None = None) -> torch.Tensor:
+    """act(x) element by element; ``params``: float32 numbers of the activation on the device (xielu: p, q)."""
+    try:
+        code = UNARY_ACTIVATIONS[name]
+    except KeyError:
+        raise KernelError(f"activation {name!r} is not built (one of {sorted(UNARY_ACTIVATIONS)})") from None
+    _dev(x, "activation input")
+    if name == "xielu":
+        if params is None or params.dtype != torch.float32 or params.numel() != 2 or not params.is_cuda:
+            raise KernelError("xielu needs its two numbers as float32 on the device")
+    out = torch.empty_like(x)
+    check(lib().psb_unary_act(x.data_ptr(), _code(x, "activation input"), out.data_ptr(), x.numel(), code, _ptr(params), _stream()),
+          "unary_act")
+    return out
+
+
+def latent_prepare(proj: torch.Tensor, positions: torch.Tensor, token_item: torch.Tensor, table: torch.Tensor,
+                   cos: torch.Tensor | None, sin: torch.Tensor | None, gain_q: torch.Tensor, gain_kv: torch.Tensor,
+                   cache: torch.Tensor, *, q_rank: int, rank: int, rot: int, rot_dims: int, heads: int, page_size: int,
+                   eps: float):
+    """One row of the fused projection [query latent | key/value latent | rotated key part | head gates] -> (normed query
+    latent [T, q_rank], sigmoid of the gates float32 [T, heads]); the normed key/value latent and the rotated key part
+    go to the token's row of the cache [pages, page_size, rank + rot]."""
+    _dev(proj, "projection output"), _dev(cache, "cache entry")
+    _i32(positions, "positions"), _i32(token_item, "token-to-item map"), _i32(table, "page table")
+    t = proj.shape[0]
+    if proj.dim() != 2 or proj.shape[1] != q_rank + rank + rot + heads:
+        raise KernelError(f"projection output must be [T, {q_rank + rank + rot + heads}], is {tuple(proj.shape)}")
+    if cache.numel() % (page_size * (rank + rot)) or cache.shape[-1] != rank + rot or cache.shape[-2] != page_size:
+        raise KernelError(f"cache entry must be [pages, .., {page_size}, {rank + rot}], is {tuple(cache.shape)}")
+    for what, g, n in (("query latent gain", gain_q, q_rank), ("key/value latent gain", gain_kv, rank)):
+        if g.dtype != torch.float32 or g.numel() != n or not g.is_cuda:
+            raise KernelError(f"{what} must be float32 [{n}] on the device")
+    max_pos = 0
+    if rot_dims:
+        if cos is None or sin is None or cos.dtype != torch.float32 or cos.shape != sin.shape or cos.dim() != 2 or cos.shape[1] != rot_dims // 2:
+            raise KernelError(f"angle tables must be float32 [positions, {rot_dims // 2}]")
+        _dev(cos, "cos table"), _dev(sin, "sin table")
+        max_pos = cos.shape[0]
+    cq = torch.empty((t, q_rank), dtype=proj.dtype, device=proj.device)
+    gate = torch.empty((t, heads), dtype=torch.float32, device=proj.device)
+    check(lib().psb_latent_prepare(proj.data_ptr(), _code(proj, "projection output"), positions.data_ptr(), token_item.data_ptr(),
+                                   table.data_ptr(), table.shape[1], _ptr(cos), _ptr(sin), gain_q.data_ptr(), gain_kv.data_ptr(),
+                                   cq.data_ptr(), gate.data_ptr(), cache.data_ptr(), _code(cache, "cache entry"), t, q_rank, rank,
+                                   rot, rot_dims, heads, page_size, cache.shape[0], max_pos, float(eps), _stream()), "latent_prepare")
+    return cq, gate
+
+
+def latent_query_rotate(q: torch.Tensor, positions: torch.Tensor, cos: torch.Tensor | None, sin: torch.Tensor | None,
+                        q_lat: torch.Tensor, *, heads: int, plain: int, rot: int, rot_dims: int, rank: int) -> None:
+    """q [T, heads * (plain + rot)]: every head's rotated part, turned by the token's position, into q_lat[:, :, rank:]
+    (float32 [T, heads, rank + rot])."""
+    _dev(q, "queries"), _dev(q_lat, "latent queries"), _i32(positions, "positions")
+    t = q.shape[0]
+    if q.dim() != 2 or q.shape[1] != heads * (plain + rot) or q_lat.dtype != torch.float32 or tuple(q_lat.shape) != (t, heads, rank + rot):
+        raise KernelError(f"queries {tuple(q.shape)} / latent queries {q_lat.dtype} {tuple(q_lat.shape)} do not fit {heads} heads of {plain}+{rot} and a latent of {rank}")
+    check(lib().psb_latent_query_rotate(q.data_ptr(), _code(q, "queries"), positions.data_ptr(), _ptr(cos), _ptr(sin), q_lat.data_ptr(),
+                                        t, heads, plain, rot, rot_dims, rank, cos.shape[0] if cos is not None else 0, _stream()),
+          "latent_query_rotate")
+
+
+def latent_attention(q_lat: torch.Tensor, cache: torch.Tensor, table: torch.Tensor, positions: torch.Tensor,
+                     token_item: torch.Tensor, gate: torch.Tensor | None, *, rank: int, page_size: int, window: int | None,
+                     scale: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """Softmax attention of latent-space queries [T, heads, rank + rot] (float32) over the cached rows
+    [pages, page_size, rank + rot]; returns sum_j p_j c_j times the head's gate, [T, heads, rank]."""
+    _dev(q_lat, "latent queries"), _dev(cache, "cache entry")
+    _i32(table, "page table"), _i32(positions, "positions"), _i32(token_item, "token-to-item map")
+    t, heads, d = q_lat.shape
+    if q_lat.dtype != torch.float32 or cache.shape[-1] != d or cache.shape[-2] != page_size or d < rank:
+        raise KernelError(f"latent queries {q_lat.dtype} {tuple(q_lat.shape)} do not fit the cache entry {tuple(cache.shape)}")
+    if gate is not None and (gate.dtype != torch.float32 or tuple(gate.shape) != (t, heads) or not gate.is_cuda):
+        raise KernelError(f"head gates must be float32 [{t}, {heads}]")
+    out = torch.empty((t, heads, rank), dtype=out_dtype, device=q_lat.device)
+    check(lib().psb_latent_attention(q_lat.data_ptr(), cache.data_ptr(), _code(cache, "cache entry"), table.data_ptr(), table.shape[1],
+                                     positions.data_ptr(), token_item.data_ptr(), _ptr(gate), out.data_ptr(), _code(out, "output"),
+                                     t, heads, rank, d - rank, page_size, cache.shape[0], int(window or 0), float(scale), _stream()),
+          "latent_attention")
+    return out
+
+
+def causal_conv(proj: torch.Tensor, bias_x: torch.Tensor, conv_w: torch.Tensor, conv_b: torch.Tensor, state: torch.Tensor,
+                ctx) -> torch.Tensor:
+    """proj [T, 2W] (gate branch, convolution branch): u[t] = conv over the branch's last K inputs (+ biases), inputs from
+    before the portion read from ``state`` [num_slots, K, W] (rows 0..K-2)."""
+    _dev(proj, "projection output"), _dev(state, "recurrent state")
+    t, two_w = proj.shape
+    w = two_w // 2
+    k = conv_w.shape[1]
+    if two_w != 2 * w or tuple(conv_w.shape) != (w, k) or state.dtype != torch.float32 or tuple(state.shape[1:]) != (k, w):
+        raise KernelError(f"projection {tuple(proj.shape)}, taps {tuple(conv_w.shape)} and state {state.dtype} {tuple(state.shape)} do not fit")
+    for what, x, n in (("branch bias", bias_x, w), ("tap weights", conv_w, w * k), ("tap bias", conv_b, w)):
+        if x.dtype != torch.float32 or x.numel() != n or not x.is_cuda or not x.is_contiguous():
+            raise KernelError(f"{what} must be float32 with {n} numbers on the device")
+    u = torch.empty((t, w), dtype=proj.dtype, device=proj.device)
+    check(lib().psb_causal_conv(proj.data_ptr(), _code(proj, "projection output"), bias_x.data_ptr(), conv_w.data_ptr(),
+                                conv_b.data_ptr(), state.data_ptr(), _i32(ctx.positions, "positions").data_ptr(),
+                                _i32(ctx.token_item, "token-to-item map").data_ptr(), _i32(ctx.item_start, "item offsets").data_ptr(),
+                                _i32(ctx.slots, "slots").data_ptr(), u.data_ptr(), t, w, k, state.shape[0], _stream()), "causal_conv")
+    return u
+
+
+def recurrence_scan(proj: torch.Tensor, u: torch.Tensor, gates: torch.Tensor, bias_y: torch.Tensor, bias_x: torch.Tensor,
+                    bias_r: torch.Tensor, bias_i: torch.Tensor, lam: torch.Tensor, state: torch.Tensor, ctx, *, blocks: int,
+                    decay: float) -> torch.Tensor:
+    """The gated linear recurrence over every portion of the step, from and to ``state`` [num_slots, K, W] (row K-1; the
+    rows before it receive the portion's last convolution inputs).  gates float32 [T, blocks, 2 * W/blocks]."""
+    _dev(proj, "projection output"), _dev(u, "convolved branch"), _dev(gates, "gate pre-activations"), _dev(state, "recurrent state")
+    t, w = u.shape
+    k = state.shape[1]
+    if proj.shape != (t, 2 * w) or u.dtype != proj.dtype or gates.dtype != torch.float32 or gates.numel() != t * 2 * w \
+            or state.dtype != torch.float32 or state.shape[2] != w or w % blocks:
+        raise KernelError("recurrence: projection, convolved branch, gates and state do not fit one another")
+    for what, x in (("gate-branch bias", bias_y), ("convolution-branch bias", bias_x), ("recurrence-gate bias", bias_r),
+                    ("input-gate bias", bias_i), ("decay parameter", lam)):
+        if x.dtype != torch.float32 or x.numel() != w or not x.is_cuda or not x.is_contiguous():
+            raise KernelError(f"{what} must be float32 [{w}] on the device")
+    out = torch.empty((t, w), dtype=proj.dtype, device=proj.device)
+    check(lib().psb_recurrence_scan(proj.data_ptr(), u.data_ptr(), _code(proj, "projection output"), gates.data_ptr(),
+                                    bias_y.data_ptr(), bias_x.data_ptr(), bias_r.data_ptr(), bias_i.data_ptr(), lam.data_ptr(),
+                                    state.data_ptr(), _i32(ctx.item_start, "item offsets").data_ptr(),
+                                    _i32(ctx.slots, "slots").data_ptr(), out.data_ptr(), ctx.num_items, w, k, blocks,
+                                    state.shape[0], float(decay), _stream()), "recurrence_scan")
+    return out

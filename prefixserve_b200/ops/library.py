@@ -119,6 +119,30 @@ _SIGNATURES: dict[str, list] = {
     "psb_pool_free": [P],
     # (S, V) -> bytes of scratch psb_sample wants
     "psb_sample_scratch_bytes": [I, I],
+    # (a, a_dtype, w, w_dtype, c, c_dtype, M, N, K, lda, ldw, ldc, batch, batch_a, batch_w, batch_c, stream)
+    "psb_gemm_nt_batched": [P, I, P, I, P, I, I, I, I, L, L, L, I, L, L, L, P],
+    # (ids, positions, token_item, item_start, slots, last_token, table, pair_table, table_dtype, out_f32, copy, copy_dtype,
+    #  T, items, H, V, buckets, mul_prev, mul_cur, num_slots, stream)
+    "psb_hashed_embedding": [P, P, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, L, L, I, P],
+    # (h, y, y_dtype, g, g_dtype, bias, gain, copy, copy_dtype, rows, H, eps, mult, stream)
+    "psb_gated_norm_add": [P, P, I, P, I, P, P, P, I, I, I, F, F, P],
+    # (x, dtype, out, total, code, params, stream)
+    "psb_unary_act": [P, I, P, L, I, P, P],
+    # (proj, dtype, positions, token_item, table, table_width, cos, sin, gain_q, gain_kv, cq_out, gate_out, cache, cache_dtype,
+    #  T, q_rank, rank, rot, rot_dims, heads, page_size, num_pages, max_positions, eps, stream)
+    "psb_latent_prepare": [P, I, P, P, P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P],
+    # (q, dtype, positions, cos, sin, q_lat, T, heads, plain, rot, rot_dims, rank, max_positions, stream)
+    "psb_latent_query_rotate": [P, I, P, P, P, P, I, I, I, I, I, I, I, P],
+    # (q_lat, cache, cache_dtype, table, table_width, positions, token_item, gate, out, out_dtype, T, heads, rank, rot,
+    #  page_size, num_pages, window, scale, stream)
+    "psb_latent_attention": [P, P, I, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
+    "psb_latent_attention_max_rank": [],
+    # (proj, dtype, bias_x, conv_w, conv_b, state, positions, token_item, item_start, slots, u_out, T, W, K, num_slots, stream)
+    "psb_causal_conv": [P, I, P, P, P, P, P, P, P, P, P, I, I, I, I, P],
+    # (proj, u, dtype, gates, bias_y, bias_x, bias_r, bias_i, lam, state, item_start, slots, out, items, W, K, blocks,
+    #  num_slots, decay, stream)
+    "psb_recurrence_scan": [P, P, I, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, F, P],
+    "psb_recurrence_max_taps": [],
 }
 
 

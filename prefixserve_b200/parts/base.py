@@ -36,6 +36,7 @@ class PagedKV:
     head_dim: int
     window: int | None = None
     key_order: str = "natural"  # how a key head's elements are ordered in the pages; writer and readers must agree
+    planes: int = 2  # 2: keys and values side by side; 1: one row per token that serves as both (a shared latent)
 
 
 @dataclass(frozen=True)
@@ -125,6 +126,16 @@ class Mixer(Part):
         return CacheNeed()
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:  # [T,H] -> [T,H]
+        raise NotImplementedError
+
+
+class Gate(Part):
+    """A gate on a sublayer's result, computed from the sublayer's input: ``forward`` returns the pre-activations
+    [T, H]; ``bias`` (float32 [H] or None) is added and the sigmoid taken by the kernel that applies the gate."""
+
+    bias: torch.Tensor | None = None
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError
 
 

@@ -5,6 +5,8 @@ The arrangement is chosen by name per layer.  Built in:
 ``pre_norm``: x = norm(h); h += mixer(x); x = norm(h); h += ffn(x)
 (prefixserve/model/llama.py:112-121, the only one that architecture uses).
 ``parallel``: both sublayers read the same stream, h += mixer(norm_a(h)) + ffn(norm_b(h)).
+``gated_post_norm``: the sublayers read the stream itself and the norm sits on their result, behind a gate computed
+from the same input: h += scale * norm_a(mixer(h) * sigmoid(gate_a(h))); then the same with the feed-forward.
 
 The residual stream h is float32.  A block takes and returns (h, pending):
 ``pending`` is a sublayer output that has not been added yet, because the sum
@@ -42,11 +44,18 @@ class Block:
         self.mixer = make("mixer", spec.mixer)
         self.ffn_norm = make("norm", spec.ffn_norm) if spec.ffn_norm is not None else None
         self.ffn = make("ffn", spec.ffn) if spec.ffn is not None else None
+        self.mixer_gate = make("gate", spec.mixer_gate) if spec.mixer_gate is not None else None
+        self.ffn_gate = make("gate", spec.ffn_gate) if spec.ffn_gate is not None and spec.ffn is not None else None
+        self.residual_scale = float(spec.residual_scale)
 
     def named_parts(self):
         parts = [("mixer_norm", self.mixer_norm), ("mixer", self.mixer)]
+        if self.mixer_gate is not None:
+            parts.append(("mixer_gate", self.mixer_gate))
         if self.ffn is not None:
             parts += [("ffn_norm", self.ffn_norm), ("ffn", self.ffn)]
+            if self.ffn_gate is not None:
+                parts.append(("ffn_gate", self.ffn_gate))
         return tuple(parts)
 
     def forward(self, h, pending, ctx: StepContext, cache: CacheView):
@@ -81,5 +90,37 @@ def parallel(block: Block, h, pending, ctx: StepContext, cache: CacheView):
     return h, fed
 
 
+STREAM_COPY = "stream_in_compute_type"  # ctx.extras: (the stream tensor, its current value in the compute type)
+
+
+def _stream_as_input(h, ctx):
+    """The stream in the type the products take: h itself on the float32 path, else the copy its last writer left
+    (the embedding, or the kernel that added the previous sublayer), made now if there is none."""
+    if ctx.compute_dtype == h.dtype:
+        return h
+    held = ctx.extras.get(STREAM_COPY)
+    if held is not None and held[0] is h:
+        return held[1]
+    return h.to(ctx.compute_dtype)
+
+
+def gated_post_norm(block: Block, h, pending, ctx: StepContext, cache: CacheView):
+    """Sublayers read the stream; each result is gated by its input, normed and added with the block's factor."""
+    if pending is not None:
+        ops.residual_add(h, pending)
+        ctx.extras.pop(STREAM_COPY, None)
+    x = _stream_as_input(h, ctx)
+    for part, gate, norm, more in ((block.mixer, block.mixer_gate, block.mixer_norm, (cache,)),
+                                   (block.ffn, block.ffn_gate, block.ffn_norm, ())):
+        if part is None:
+            continue
+        y = part.forward(x, ctx, *more)
+        g = gate.forward(x, ctx) if gate is not None else None
+        x = norm.add_normed(h, y, ctx, gate=g, gate_bias=gate.bias if gate is not None else None, scale=block.residual_scale)
+    ctx.extras[STREAM_COPY] = (h, x)
+    return h, None
+
+
 register_arrangement("pre_norm", pre_norm)
+register_arrangement("gated_post_norm", gated_post_norm)
 register_arrangement("parallel", parallel)

@@ -33,6 +33,43 @@ class TokenEmbedding(Part):
         return ops.embedding(token_ids, self.table)
 
 
+class HashedPairEmbedding(Part):
+    """Token embedding plus a row of a second table chosen by a hash of (previous token, token):
+    row (previous * mul_prev + token * mul_cur) mod buckets, and the table's last row (number ``buckets``) for the
+    first token of a sequence.  The previous token of a portion's first token is not in the step: it is carried per
+    request in a one-word state, which makes this an embedding with a cache entry of its own (``uses_step``)."""
+
+    graph_safe = True  # device work depends only on tensor shapes and device-side inputs
+    uses_step = True   # forward_step(ctx, cache) instead of forward(token_ids)
+
+    def __init__(self, params):
+        super().__init__(params)
+        self.vocab = int(params["vocab_size"])
+        self.hidden = int(params["hidden_size"])
+        self.buckets = int(params["buckets"])
+        self.mul_prev = int(params["mul_prev"])
+        self.mul_cur = int(params["mul_cur"])
+        self.table: torch.Tensor | None = None
+        self.pair_table: torch.Tensor | None = None
+
+    def param_specs(self):
+        return {"weight": ParamSpec((self.vocab, self.hidden)), "pair_weight": ParamSpec((self.buckets + 1, self.hidden))}
+
+    def cache_need(self):
+        from .base import CacheNeed, FixedState
+        return CacheNeed(state=FixedState((1,), torch.int32))
+
+    def load(self, tensors, *, compute_dtype, device):
+        self.table = tensors["weight"].contiguous()
+        self.pair_table = tensors["pair_weight"].to(self.table.dtype).contiguous()
+
+    def forward_step(self, ctx, cache):
+        """(float32 stream [T, H], the same in the compute type or None on the float32 path)."""
+        return ops.hashed_embedding(ctx.token_ids, ctx.positions, ctx.token_item, ctx.item_start, ctx.slots,
+                                    cache.state.view(-1), self.table, self.pair_table, mul_prev=self.mul_prev,
+                                    mul_cur=self.mul_cur, copy_dtype=ctx.compute_dtype)
+
+
 class LMHead(Part):
     graph_safe = True  # device work depends only on tensor shapes and device-side inputs
     takes_deferred_input = True  # x goes to one product only, which may do the norm in front of it itself
@@ -59,4 +96,5 @@ class LMHead(Part):
 
 
 register_embedding("token_embedding", TokenEmbedding, replace=True)
+register_embedding("hashed_pair_embedding", HashedPairEmbedding, replace=True)
 register_head("lm_head", LMHead, replace=True)

@@ -41,4 +41,38 @@ class GatedMLP(FeedForward):
         return ops.last_product(ops.gated_linear(x, self.w_gate_up, self.activation), self.w_down, ctx)
 
 
+class DenseMLP(FeedForward):
+    """Feed-forward without a gate branch: down(act(up(x))).  ``activation``: silu, gelu_tanh, or xielu, which brings
+    two learned numbers of its own (tensor ``act`` [2])."""
+
+    graph_safe = True  # device work depends only on tensor shapes and device-side inputs
+
+    def __init__(self, params):
+        super().__init__(params)
+        self.hidden = int(params["hidden_size"])
+        self.inter = int(params["intermediate_size"])
+        self.activation = str(params.get("activation", "gelu_tanh"))
+        if self.activation not in ops.UNARY_ACTIVATIONS:
+            raise ValueError(f"activation {self.activation!r} is not built (one of {sorted(ops.UNARY_ACTIVATIONS)})")
+        self.w_up: torch.Tensor | None = None
+        self.w_down: torch.Tensor | None = None
+        self.act_params: torch.Tensor | None = None
+
+    def param_specs(self):
+        specs = {"up_proj": ParamSpec((self.inter, self.hidden)), "down_proj": ParamSpec((self.hidden, self.inter))}
+        if self.activation == "xielu":
+            specs["act"] = ParamSpec((2,), role="vector", init="normal")
+        return specs
+
+    def load(self, tensors, *, compute_dtype, device):
+        self.w_up = tensors["up_proj"].contiguous()
+        self.w_down = tensors["down_proj"].contiguous()
+        if self.activation == "xielu":
+            self.act_params = tensors["act"].to(device=device, dtype=torch.float32).contiguous()
+
+    def forward(self, x, ctx: StepContext):
+        return ops.linear(ops.activation(ops.linear(x, self.w_up), self.activation, self.act_params), self.w_down)
+
+
 register_ffn("gated_mlp", GatedMLP, replace=True)
+register_ffn("mlp", DenseMLP, replace=True)

@@ -80,7 +80,10 @@ class DecoderModel:
                 need = self.blocks[call.layer].mixer.cache_need()
                 if needs[call.cache] != need:
                     raise ValueError(f"layer {call.layer} reads cache entry {call.cache} but needs {need}, entry holds {needs[call.cache]}")
-        return [n if n is not None else CacheNeed() for n in needs]
+        needs = [n if n is not None else CacheNeed() for n in needs]
+        if getattr(self.embedding, "uses_step", False):  # an embedding that carries something per request: the entry after the layers'
+            needs.append(self.embedding.cache_need())
+        return needs
 
     # ---- one step ----------------------------------------------------------
     def forward(self, ctx: StepContext, cache_view: Callable[[int, bool], CacheView], rows: torch.Tensor) -> torch.Tensor:
@@ -94,7 +97,13 @@ class DecoderModel:
                                    and all(getattr(n, "takes_pending_products", False) for n in norms))
         if self._lazy_products:
             ctx.extras["lazy_products"] = True
-        h = self.embedding.forward(ctx.token_ids)
+        if getattr(self.embedding, "uses_step", False):
+            from .block import STREAM_COPY
+            h, copy = self.embedding.forward_step(ctx, cache_view(self.spec.num_cache_entries, True))
+            if copy is not None:
+                ctx.extras[STREAM_COPY] = (h, copy)
+        else:
+            h = self.embedding.forward(ctx.token_ids)
         pending = None
         for at, call in enumerate(self.spec.schedule):
             if _NVTX:  # PSB200_NVTX=1: a named range per run-list entry for timeline tools

@@ -23,16 +23,26 @@ class RMSNorm(Norm):
         super().__init__(params)
         self.size = int(params["size"])
         self.eps = float(params["eps"])
+        # zero_centred: the checkpoint stores the gain as an offset from one (the rows are multiplied by 1 + weight)
+        self.zero_centred = bool(params.get("zero_centred", False))
         self.gain: torch.Tensor | None = None
 
     def param_specs(self):
-        return {"weight": ParamSpec((self.size,), role="vector", init="ones")}
+        return {"weight": ParamSpec((self.size,), role="vector", init="normal" if self.zero_centred else "ones")}
 
     def load(self, tensors, *, compute_dtype, device):
-        self.gain = tensors["weight"].to(device=device, dtype=torch.float32).contiguous()
+        gain = tensors["weight"].to(device=device, dtype=torch.float32)
+        self.gain = (1.0 + gain if self.zero_centred else gain).contiguous()
 
     def forward(self, h, delta, ctx: StepContext, rows=None):
         return ops.add_rmsnorm(h, delta, self.gain, self.eps, ctx.compute_dtype, rows)
+
+    def add_normed(self, h, y, ctx: StepContext, *, gate=None, gate_bias=None, scale: float = 1.0):
+        """The norm on a sublayer's result instead of its input: h += scale * norm(y * sigmoid(gate + gate_bias)) in
+        place (``gate`` None: norm(y)).  Returns the new stream in the compute type for the next sublayer's products
+        (h itself on the float32 path)."""
+        copy = ops.gated_norm_add(h, y, gate, gate_bias, self.gain, self.eps, scale, ctx.compute_dtype)
+        return h if copy is None else copy
 
     def defer(self, h, delta, ctx: StepContext, rows=None):
         return ops.NormedRows(h, delta, self.gain, self.eps, ctx.compute_dtype, rows)

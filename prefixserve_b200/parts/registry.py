@@ -9,7 +9,7 @@ from typing import Any, Callable, Mapping
 from ..config.spec import PartSpec
 
 _KINDS: dict[str, dict[str, Callable[..., Any]]] = {
-    "mixer": {}, "ffn": {}, "norm": {}, "position": {}, "embedding": {}, "head": {},
+    "mixer": {}, "ffn": {}, "norm": {}, "position": {}, "embedding": {}, "head": {}, "gate": {},
 }
 
 
@@ -34,6 +34,10 @@ def register_norm(kind: str, factory: Callable[..., Any], *, replace: bool = Fal
 
 def register_position(kind: str, factory: Callable[..., Any], *, replace: bool = False) -> None:
     _register("position", kind, factory, replace)
+
+
+def register_gate(kind: str, factory: Callable[..., Any], *, replace: bool = False) -> None:
+    _register("gate", kind, factory, replace)
 
 
 def register_embedding(kind: str, factory: Callable[..., Any], *, replace: bool = False) -> None:
