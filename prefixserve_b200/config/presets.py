@@ -7,6 +7,7 @@ configuration, never from this file directly.
 from __future__ import annotations
 
 from .llama import LlamaConfig
+from .registry import architecture_of
 
 _LLAMA3_ROPE = {"rope_type": "llama3", "low_freq_factor": 1.0, "high_freq_factor": 4.0,
                 "original_max_position_embeddings": 8192}
@@ -45,8 +46,41 @@ PRESETS: dict[str, dict] = {
 }
 
 
-def preset(name: str) -> LlamaConfig:
+def _nerenex(width: int, vocab: int, groups: int, heads: int, ff: int, window: int, recurrent_width: int) -> dict:
+    """``groups`` times (recurrence, recurrence, latent attention), every layer with a dense feed-forward."""
+    attention = {"type": "latent_attention", "mlp": {"kind": "dense", "ff": ff},
+                 "mixer": {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": 3 * width // 4, "kv_rank": 512,
+                           "scale": 192 ** -0.5, "mask": {"size": window}, "rot": {"base": 10000.0, "dims": 64}}}
+    recurrent = {"type": "rglru", "mlp": {"kind": "dense", "ff": ff},
+                 "mixer": {"width": recurrent_width, "blocks": heads, "conv": 4}}
+    return {"architecture": "Nerenex", "vocab": vocab, "width": width, "residual_mult": 0.5, "norm": {"eps": 1e-6},
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 1000003, "mul_cur": 8191}},
+            "layers": [recurrent, recurrent, attention] * groups}
+
+
+PRESETS.update({
+    "nerenex-tiny": {
+        "architecture": "Nerenex", "vocab": 256, "width": 64, "residual_mult": 0.5, "norm": {"eps": 1e-6},
+        "embedding": {"bigram": {"buckets": 251, "mul_prev": 31, "mul_cur": 7}},
+        "layers": [
+            {"type": "rglru", "mixer": {"width": 96, "blocks": 3, "conv": 4}, "mlp": {"kind": "dense", "ff": 128}},
+            {"type": "latent_attention", "mlp": None,
+             "mixer": {"heads": 4, "dim": 16, "rot_dim": 8, "vdim": 24, "q_rank": 48, "kv_rank": 32, "scale": 0.2,
+                       "mask": {"size": 24}, "rot": {"base": 10000.0, "dims": 8}}},
+        ],
+    },
+    # layer sizes of a 1B- and an 8B-class decoder (width, heads, feed-forward), for the benchmarks
+    "nerenex-2048": _nerenex(2048, 32768, 4, 16, 8192, 1024, 2560),
+    "nerenex-4096": _nerenex(4096, 32768, 2, 32, 14336, 2048, 4096),
+})
+
+
+def preset(name: str):
+    """The typed configuration of a preset, read by its architecture's own reader."""
     try:
-        return LlamaConfig.from_dicts(PRESETS[name])
+        raw = PRESETS[name]
     except KeyError:
         raise ValueError(f"no preset {name!r}; known: {sorted(PRESETS)}") from None
+    if "architecture" not in raw and "architectures" not in raw:
+        return LlamaConfig.from_dicts(raw)
+    return architecture_of(raw).read_config(raw, None)
