@@ -762,6 +762,138 @@ def kernel_costs(base: dict) -> list[tuple[str, float, float]]:
     ]
 
 
+# ------------------------------------------------------------------ another design beside the closest Llama
+NERENEX_SIZES = {"2048": ("nerenex-2048", "1b"), "4096": ("nerenex-4096", "8b")}
+
+
+def run_nerenex(args) -> dict:
+    """--workload nerenex: prefill and decode throughput of the Nerenex design (recurrence, recurrence, latent attention
+    with a window; gated post-norm blocks; random weights) at layer sizes of a 1B- and an 8B-class decoder, beside a
+    Llama of the same width and number of layers, device-timed, with the time of every kernel name in one prefill step
+    and one decode step (torch profiler; those steps are not the timed ones)."""
+    import re
+
+    import numpy as np
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    from prefixserve_b200.config.presets import PRESETS, preset
+    from prefixserve_b200.engine import Engine, EngineConfig, StepItem
+    from prefixserve_b200.weights import write_random_model
+
+    prompt, context, batches = 2048, args.context if "--context" in sys.argv else 2048, (8, 32)
+    steps, warmup = min(args.steps, 32), max(3, min(args.warmup, 8))
+    out = {"workload": "nerenex", "dtype": "bf16", "data": "synthetic", "prompt": prompt, "context": context, "steps": steps,
+           "warmup": warmup, "timing": "CUDA events; weights of every model exceed L2", "peaks": peaks(), "sizes": {}}
+    for size in ([args.model] if args.model in NERENEX_SIZES else sorted(NERENEX_SIZES)):
+        own_name, llama_name = NERENEX_SIZES[size]
+        n_layers = len(PRESETS[own_name]["layers"])
+        entry = out["sizes"][size] = {}
+        for which in ("nerenex", "llama"):
+            if which == "nerenex":
+                cfg = preset(own_name)
+                vocab = cfg.vocab
+            else:
+                from prefixserve_b200.config import LlamaConfig
+                cfg = LlamaConfig.from_dicts(dict(PRESETS[SIZES[llama_name]], num_hidden_layers=n_layers, vocab_size=32768))
+                vocab = cfg.vocab_size
+            work = Path(tempfile.mkdtemp(prefix="psb200-bench-"))
+            try:
+                write_random_model(work, cfg, 0, std=0.02, dtype=torch.bfloat16, device="cuda")
+                max_b = max(batches)
+                engine = Engine(EngineConfig(model_path=work, dtype=torch.bfloat16, max_num_seqs=max_b, max_prefill_tokens=prompt,
+                                             max_seq_len=context + 64, num_blocks=max_b * ((context + 64) // PAGE + 1) + 8,
+                                             page_size=PAGE, enable_prefix_cache=False, use_cuda_graphs=not args.no_graphs))
+                runner, cache = engine.runner, engine.cache
+                rng = np.random.RandomState(0)
+
+                def portion(slot, at, n, want=()):
+                    cache.reserve(slot, at + n)
+                    logits = runner.step([StepItem(slot, at, rng.randint(0, vocab, size=n).astype(np.int32), want)])
+                    cache.advance(slot, at + n)
+                    return logits
+
+                def prefill_once() -> float:
+                    slot = cache.open()
+                    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    torch.cuda.synchronize()
+                    t0.record()
+                    portion(slot, 0, prompt, (prompt - 1,))
+                    t1.record()
+                    torch.cuda.synchronize()
+                    cache.close(slot)
+                    return t0.elapsed_time(t1)
+
+                def decode(slots) -> None:
+                    items = []
+                    for s in slots:
+                        p = cache.position(s)
+                        cache.reserve(s, p + 1)
+                        items.append(StepItem(s, p, rng.randint(0, vocab, size=1).astype(np.int32), (0,)))
+                    runner.step(items)
+                    for it in items:
+                        cache.advance(it.slot, it.start + 1)
+
+                def kernels_of(fn) -> dict:
+                    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                        fn()
+                        torch.cuda.synchronize()
+                    rows: dict[str, list] = {}
+                    for e in prof.events():
+                        if e.device_type.name == "CUDA" and e.device_time_total > 0 and not e.name.startswith("Memcpy") \
+                                and not e.name.startswith("Memset"):
+                            m = re.search(r"(\w+_kernel)", e.name)
+                            row = rows.setdefault(m.group(1) if m else e.name[:40], [0, 0.0])
+                            row[0] += 1
+                            row[1] += e.device_time_total
+                    return {k: {"launches": n, "us": round(t, 1)} for k, (n, t) in sorted(rows.items(), key=lambda kv: -kv[1][1])}
+
+                for _ in range(warmup):
+                    prefill_once()
+                with ClockSampler() as clocks:
+                    times = sorted(prefill_once() for _ in range(5))
+                res = {"weight_bytes": engine.weight_bytes(), "layers": n_layers,
+                       "prefill_ms": round(times[2], 3), "prefill_tok_s": round(prompt / times[2] * 1e3, 1), "clocks": clocks.summary()}
+                res["prefill_kernels"] = kernels_of(prefill_once)
+                for b in batches:
+                    slots = []
+                    for _ in range(b):
+                        slot = cache.open()
+                        at = 0
+                        while at < context - steps - warmup - 1:
+                            n = min(prompt, context - steps - warmup - 1 - at)
+                            portion(slot, at, n)
+                            at += n
+                        slots.append(slot)
+                    for _ in range(warmup):
+                        decode(slots)
+                    torch.cuda.synchronize()
+                    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    t0.record()
+                    for _ in range(steps):
+                        decode(slots)
+                    t1.record()
+                    torch.cuda.synchronize()
+                    ms = t0.elapsed_time(t1) / steps
+                    res[f"decode_b{b}_ms"] = round(ms, 4)
+                    res[f"decode_b{b}_tok_s"] = round(b / ms * 1e3, 1)
+                    res[f"decode_b{b}_weights_bound_ms"] = round(res["weight_bytes"] / (out["peaks"]["hbm_gbs"] * 1e9) * 1e3, 4)
+                    if b == batches[0]:
+                        res["decode_kernels"] = kernels_of(lambda: decode(slots))
+                    for s in slots:
+                        cache.close(s)
+                engine.check_device_status()
+                entry[which] = res
+                del engine, runner, cache
+                import gc
+                gc.collect()
+                torch.cuda.empty_cache()
+            finally:
+                shutil.rmtree(work, ignore_errors=True)
+    return out
+
+
+
 def _no_device(args) -> bool:
     """Neither arm has a CPU path: without a CUDA device, one line says so instead of a stack of CUDA errors."""
     import torch
@@ -795,10 +927,11 @@ def main() -> int:
     p.add_argument("--profile", action="store_true",
                    help="--timeline plus, per kernel, the bytes and flops it has to do in the step and the fraction of the "
                         "measured peak that its time inside the step amounts to")
-    p.add_argument("--workload", choices=["decode", "shared-prefix", "mixed"], default="decode",
+    p.add_argument("--workload", choices=["decode", "shared-prefix", "mixed", "nerenex"], default="decode",
                    help="decode: the headline line.  shared-prefix: 64 requests over 4 system prefixes through the entry "
-                        "point, prefix cache on and off.  mixed: steps of one 512-token prompt portion beside 64 decoded tokens")
-    p.add_argument("--model", choices=sorted(SIZES), default=None,
+                        "point, prefix cache on and off.  mixed: steps of one 512-token prompt portion beside 64 decoded tokens.  "
+                        "nerenex: prefill and decode of the Nerenex design beside a Llama of the same width and depth (--model 2048|4096)")
+    p.add_argument("--model", choices=sorted(SIZES) + sorted(NERENEX_SIZES), default=None,
                    help="layer sizes for --workload shared-prefix (8b) / mixed (3b), and for --only decode (the headline stays 1b)")
     p.add_argument("--requests", type=int, default=64, help="requests of --workload shared-prefix")
     p.add_argument("--prompt", type=int, default=None,
@@ -833,6 +966,10 @@ def main() -> int:
             return 0
         if _no_device(args):
             return 1
+        if args.workload == "nerenex":
+            result = run_nerenex(args)
+            print(json.dumps(result))
+            return 0
         args.model = args.model or ("8b" if args.workload == "shared-prefix" else "3b")
         args.layers = None if args.layers == FULL_LAYERS and "--layers" not in sys.argv else args.layers
         result = run_shared_prefix(args) if args.workload == "shared-prefix" else run_mixed(args)

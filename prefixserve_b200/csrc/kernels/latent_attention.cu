@@ -14,9 +14,10 @@
 //   sigmoid of the gates (float32).  The norms are x / sqrt(mean(x^2) + eps) * gain in float32.
 // latent_query_rotate_kernel: the rotated part of every head's query, turned by the token's position, into the
 //   tail of the float32 query rows [T, heads, rank + rot] whose first ``rank`` columns the batched product fills.
-// latent_attention_kernel: one warp per (token, head) walks the visible keys in runs of 32 aligned to absolute
-//   positions (the order of every sum depends on the token's position only), scores and softmax in float32, the
-//   output (times the head's gate) accumulated in registers.
+// latent_attention_kernel: one block per (token, head) walks the visible keys in runs of 32 aligned to absolute
+//   positions, the runs dealt out to its four warps in turn and the four partial results joined in warp order (the
+//   order of every sum depends on the token's position only), scores and softmax in float32, the output (times the
+//   head's gate) accumulated in registers.
 //
 // The rotation pairs element 2i with 2i+1 for i < rot_dims/2 (the rest of the rotated part passes through), angle
 // tables float32 [positions, rot_dims/2].
@@ -126,34 +127,69 @@ __global__ void latent_query_rotate_kernel(const T* __restrict__ q, const int32_
 
 constexpr int WARPS = 4;
 
+// dot of a float32 query (shared memory) with a cached row, eight elements a load where the row allows it
+template <typename TKV>
+__device__ __forceinline__ float row_dot(const float* __restrict__ qs, const TKV* __restrict__ krow, int D, bool vec) {
+  float dot = 0.f;
+  int d = 0;
+  if (vec) {
+    for (; d + 8 <= D; d += 8) {
+      float k[8];
+      if constexpr (sizeof(TKV) == 2) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(krow + d);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __bfloat1622float2(h2[i]);
+          k[2 * i] = f.x;
+          k[2 * i + 1] = f.y;
+        }
+      } else {
+        const float4 a = *reinterpret_cast<const float4*>(krow + d), b = *reinterpret_cast<const float4*>(krow + d + 4);
+        k[0] = a.x; k[1] = a.y; k[2] = a.z; k[3] = a.w; k[4] = b.x; k[5] = b.y; k[6] = b.z; k[7] = b.w;
+      }
+      const float4 q0 = *reinterpret_cast<const float4*>(qs + d), q1 = *reinterpret_cast<const float4*>(qs + d + 4);
+      dot = fmaf(q0.x, k[0], dot); dot = fmaf(q0.y, k[1], dot); dot = fmaf(q0.z, k[2], dot); dot = fmaf(q0.w, k[3], dot);
+      dot = fmaf(q1.x, k[4], dot); dot = fmaf(q1.y, k[5], dot); dot = fmaf(q1.z, k[6], dot); dot = fmaf(q1.w, k[7], dot);
+    }
+  }
+  for (; d < D; ++d) dot = fmaf(qs[d], to_float<TKV>(krow[d]), dot);
+  return dot;
+}
+
+// One block per (token, head).  Its four warps take the runs of 32 keys in turn (run r goes to warp r mod 4), each
+// with a running maximum, sum and output of its own; the four are then joined in warp order.  Lane l of a warp owns
+// output columns 2l, 2l+1, 2l+64, ... (pairs, so that a bfloat16 row is read four bytes at a time).
 template <typename TKV, typename TO, int NACC>
 __global__ void __launch_bounds__(WARPS * 32)
 latent_attention_kernel(const float* __restrict__ q_lat, const TKV* __restrict__ cache, const int32_t* __restrict__ table,
                         int table_width, const int32_t* __restrict__ positions, const int32_t* __restrict__ token_item,
                         const float* __restrict__ gate, TO* __restrict__ out, int T_tokens, int heads, int rank, int rot,
                         int page_size, int num_pages, int window, float scale) {
-  extern __shared__ float qs_all[];
+  extern __shared__ __align__(16) float smem[];
   pdl_trigger();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int D = rank + rot;
-  float* qs = qs_all + (size_t)warp * D;
-  const long long unit = (long long)blockIdx.x * WARPS + warp;
-  if (unit >= (long long)T_tokens * heads) return;
-  const int t = (int)(unit / heads), h = (int)(unit - (long long)t * heads);
+  const int Dpad = (D + 3) & ~3;
+  float* qs = smem;                         // [Dpad]
+  float* part_ml = smem + Dpad;             // [WARPS][2]
+  float* part_o = part_ml + 2 * WARPS;      // [WARPS][rank]
+  const int t = blockIdx.x / heads, h = blockIdx.x - t * heads;
   const int p = positions[t];
   const int32_t* pages = table + (size_t)token_item[t] * table_width;
   const float* qrow = q_lat + ((size_t)t * heads + h) * D;
-  for (int d = lane; d < D; d += 32) qs[d] = qrow[d];
-  __syncwarp();
+  for (int d = threadIdx.x; d < D; d += blockDim.x) qs[d] = qrow[d];
+  __syncthreads();
 
+  const bool vec = (D % 8 == 0);  // rows then start on 16-byte boundaries (the cache's base is aligned by its allocator)
   const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
   float m = -FLT_MAX, l = 0.f;
-  float acc[NACC];
+  float acc[NACC][2];
 #pragma unroll
-  for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
+  for (int i = 0; i < NACC; ++i) acc[i][0] = acc[i][1] = 0.f;
 
-  for (int base = lo & ~31; base <= p; base += 32) {
+  for (int base = (lo & ~31) + 32 * warp; base <= p; base += 32 * WARPS) {
     const int key = base + lane;
     const bool live = key >= lo && key <= p;
     long long off = -1;  // element offset of this lane's key row
@@ -162,20 +198,19 @@ latent_attention_kernel(const float* __restrict__ q_lat, const TKV* __restrict__
       const int page = pages[key / page_size];
       if (page >= 0 && page < num_pages) {
         off = ((long long)page * page_size + (key % page_size)) * D;
-        const TKV* krow = cache + off;
-        float dot = 0.f;
-        for (int d = 0; d < D; ++d) dot = fmaf(qs[d], to_float<TKV>(krow[d]), dot);
-        s = dot * scale;
+        s = row_dot<TKV>(qs, cache + off, D, vec) * scale;
       }
     }
-    const float run_max = warp_max(s);
-    const float m_new = fmaxf(m, run_max);
+    const float m_new = fmaxf(m, warp_max(s));
     const float alpha = expf(m - m_new);   // first run: exp(-huge) = 0
     const float pr = off >= 0 ? expf(s - m_new) : 0.f;
     l = l * alpha + warp_sum(pr);
     m = m_new;
 #pragma unroll
-    for (int i = 0; i < NACC; ++i) acc[i] *= alpha;
+    for (int i = 0; i < NACC; ++i) {
+      acc[i][0] *= alpha;
+      acc[i][1] *= alpha;
+    }
     const int n_live = min(32, p - base + 1);
     for (int j = 0; j < n_live; ++j) {
       const float pj = __shfl_sync(0xffffffffu, pr, j);
@@ -184,17 +219,52 @@ latent_attention_kernel(const float* __restrict__ q_lat, const TKV* __restrict__
       const TKV* vrow = cache + oj;
 #pragma unroll
       for (int i = 0; i < NACC; ++i) {
-        const int d = lane + 32 * i;
-        if (d < rank) acc[i] = fmaf(pj, to_float<TKV>(vrow[d]), acc[i]);
+        const int d = 2 * lane + 64 * i;
+        if (d + 1 < rank) {
+          if constexpr (sizeof(TKV) == 2) {
+            if ((D & 1) == 0) {
+              const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(vrow + d));
+              acc[i][0] = fmaf(pj, v.x, acc[i][0]);
+              acc[i][1] = fmaf(pj, v.y, acc[i][1]);
+              continue;
+            }
+          }
+          acc[i][0] = fmaf(pj, to_float<TKV>(vrow[d]), acc[i][0]);
+          acc[i][1] = fmaf(pj, to_float<TKV>(vrow[d + 1]), acc[i][1]);
+        } else if (d < rank) {
+          acc[i][0] = fmaf(pj, to_float<TKV>(vrow[d]), acc[i][0]);
+        }
       }
     }
   }
-  const float w = (gate ? gate[(size_t)t * heads + h] : 1.f) / l;
-  TO* orow = out + ((size_t)t * heads + h) * rank;
+  // join the four warps' partial results in warp order
+  if (lane == 0) {
+    part_ml[2 * warp] = m;
+    part_ml[2 * warp + 1] = l;
+  }
 #pragma unroll
   for (int i = 0; i < NACC; ++i) {
-    const int d = lane + 32 * i;
-    if (d < rank) orow[d] = from_float<TO>(acc[i] * w);
+    const int d = 2 * lane + 64 * i;
+    if (d < rank) part_o[(size_t)warp * rank + d] = acc[i][0];
+    if (d + 1 < rank) part_o[(size_t)warp * rank + d + 1] = acc[i][1];
+  }
+  __syncthreads();
+  float m_all = -FLT_MAX;
+#pragma unroll
+  for (int w = 0; w < WARPS; ++w) m_all = fmaxf(m_all, part_ml[2 * w]);
+  float f[WARPS], l_all = 0.f;
+#pragma unroll
+  for (int w = 0; w < WARPS; ++w) {
+    f[w] = part_ml[2 * w + 1] > 0.f ? expf(part_ml[2 * w] - m_all) : 0.f;
+    l_all += part_ml[2 * w + 1] * f[w];
+  }
+  const float wgt = (gate ? gate[(size_t)t * heads + h] : 1.f) / l_all;
+  TO* orow = out + ((size_t)t * heads + h) * rank;
+  for (int d = threadIdx.x; d < rank; d += blockDim.x) {
+    float v = 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) v += part_o[(size_t)w * rank + d] * f[w];
+    orow[d] = from_float<TO>(v * wgt);
   }
 }
 
@@ -249,10 +319,10 @@ PSB_API int psb_latent_attention(const void* q_lat, const void* cache, int cache
   if (page_size < 1 || num_pages < 1 || table_width < 1) PSB_REFUSE("latent_attention: bad paging (page_size=%d pages=%d width=%d)", page_size, num_pages, table_width);
   if (window < 0) PSB_REFUSE("latent_attention: negative window");
   if (T == 0) return 0;
-  const long long units = (long long)T * heads;
-  const long long blocks = (units + WARPS - 1) / WARPS;
+  const long long blocks = (long long)T * heads;
   if (blocks > 0x7fffffffLL) PSB_REFUSE("latent_attention: batch too large");
-  const size_t smem = (size_t)WARPS * (rank + rot) * sizeof(float);
+  if ((uintptr_t)cache & 15) PSB_REFUSE("latent_attention: the cache entry must be 16-byte aligned");
+  const size_t smem = ((size_t)((rank + rot + 3) & ~3) + 2 * WARPS + (size_t)WARPS * rank) * sizeof(float);
 #define LATENT_LAUNCH(NACC)                                                                                              \
   PSB_DISPATCH_DTYPE(cache_dtype, TKV, {                                                                                 \
     PSB_DISPATCH_DTYPE(out_dtype, TO, {                                                                                  \
@@ -262,10 +332,10 @@ PSB_API int psb_latent_attention(const void* q_lat, const void* cache, int cache
                  window, scale);                                                                                         \
     });                                                                                                                  \
   })
-  if (rank <= 128) { LATENT_LAUNCH(4); }
-  else if (rank <= 256) { LATENT_LAUNCH(8); }
-  else if (rank <= 512) { LATENT_LAUNCH(16); }
-  else { LATENT_LAUNCH(32); }
+  if (rank <= 128) { LATENT_LAUNCH(2); }        // NACC pairs of columns a lane: 64 columns each
+  else if (rank <= 256) { LATENT_LAUNCH(4); }
+  else if (rank <= 512) { LATENT_LAUNCH(8); }
+  else { LATENT_LAUNCH(16); }
 #undef LATENT_LAUNCH
   PSB_LAUNCH_CHECK("latent_attention");
   return 0;

@@ -10,11 +10,13 @@
 //   u_t[c] = sum_k w[c][k] x_(t-K+1+k)[c] + b[c]         (w's last column multiplies the current token)
 // taking inputs from before the portion out of the slot.  A batched product then gives the pre-activations of the
 // two gates, block by block of the channels ([T, blocks, 2 * W/blocks] float32: recurrence gate, input gate), and
-// recurrence_scan_kernel runs, one thread per (request, channel) over the portion's tokens in order:
+// recurrence_scan_kernel runs, one thread per (portion or chunk of it, channel) over its tokens in order:
 //   r = sigmoid(.. + br), i = sigmoid(.. + bi), a = exp(-decay * r * softplus(lam)),
 //   S = a S + sqrt(1 - a^2) * i * u,        out = S * gelu_tanh(gate branch + bias)
 // all in float32; then it leaves S and the portion's last K-1 convolution inputs in the slot (after every block of
-// the convolution kernel has finished reading the old ones: a later launch).
+// the convolution kernel has finished reading the old ones: a later launch).  A long portion is cut into chunks
+// that run side by side: S -> a S + b composes, so a first pass (recurrence_chunk_kernel) reduces every chunk to
+// one such map and the second pass folds the maps of the chunks in front of its own before it starts.
 #include "common.cuh"
 
 namespace {
@@ -52,23 +54,74 @@ __global__ void causal_conv_kernel(const T* __restrict__ proj, const float* __re
   }
 }
 
+// Which portion and which of its chunks a block works on: chunks of ``chunk`` tokens are numbered through the step's
+// portions in order.  False when the number is beyond the last chunk (the grid is sized by an upper bound).
+__device__ __forceinline__ bool find_chunk(const int32_t* __restrict__ item_start, int items, int chunk, int g, int& item,
+                                           int& index, int& count) {
+  for (int i = 0; i < items; ++i) {
+    const int n = item_start[i + 1] - item_start[i];
+    const int c = (n + chunk - 1) / chunk;
+    if (g < c) {
+      item = i;
+      index = g;
+      count = c;
+      return true;
+    }
+    g -= c;
+  }
+  return false;
+}
+
+// First pass over a portion cut into chunks: every chunk's decay product A and its result B from a zero state, so
+// that the state entering chunk k is the fold of S -> A_j S + B_j over the chunks before it.  Portions of one chunk
+// are skipped (the second pass starts them from the slot's state directly).
+template <typename T>
+__global__ void recurrence_chunk_kernel(const T* __restrict__ u, const float* __restrict__ gates,
+                                        const float* __restrict__ bias_r, const float* __restrict__ bias_i,
+                                        const float* __restrict__ lam, const int32_t* __restrict__ item_start,
+                                        float2* __restrict__ carry, int items, int W, int block_width, int chunk, float decay) {
+  pdl_trigger();
+  pdl_wait();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  int item, index, count;
+  if (c >= W || !find_chunk(item_start, items, chunk, blockIdx.y, item, index, count) || count == 1) return;
+  const int t0 = item_start[item] + index * chunk, t1 = min(t0 + chunk, item_start[item + 1]);
+  const int blk = c / block_width, j = c - blk * block_width;
+  const float* g = gates + (size_t)blk * 2 * block_width + j;
+  const float br = bias_r[c], bi = bias_i[c];
+  const float rate = decay * softplusf_(lam[c]);
+  float A = 1.f, B = 0.f;
+  for (int t = t0; t < t1; ++t) {
+    const float r = sigmoidf_(g[(size_t)t * 2 * W] + br), i = sigmoidf_(g[(size_t)t * 2 * W + block_width] + bi);
+    const float a = expf(-rate * r);
+    B = a * B + sqrtf(1.f - a * a) * (i * to_float<T>(u[(size_t)t * W + c]));
+    A *= a;
+  }
+  carry[(size_t)blockIdx.y * W + c] = make_float2(A, B);
+}
+
 template <typename T>
 __global__ void recurrence_scan_kernel(const T* __restrict__ proj, const T* __restrict__ u, const float* __restrict__ gates,
                                        const float* __restrict__ bias_y, const float* __restrict__ bias_x,
                                        const float* __restrict__ bias_r, const float* __restrict__ bias_i,
                                        const float* __restrict__ lam, float* __restrict__ state,
                                        const int32_t* __restrict__ item_start, const int32_t* __restrict__ slots,
-                                       T* __restrict__ out, int W, int K, int block_width, int num_slots, float decay) {
+                                       const float2* __restrict__ carry, T* __restrict__ out, int items, int W, int K,
+                                       int block_width, int num_slots, int chunk, float decay) {
   pdl_trigger();
   pdl_wait();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  const int item = blockIdx.y;
-  if (c >= W) return;
+  int item, index, count;
+  if (c >= W || !find_chunk(item_start, items, chunk, blockIdx.y, item, index, count)) return;
   const int slot = slots[item];
   if (slot < 0 || slot >= num_slots) return;
-  const int t0 = item_start[item], t1 = item_start[item + 1];
+  const int t0 = item_start[item] + index * chunk, t1 = min(t0 + chunk, item_start[item + 1]);
   float* mine = state + (size_t)slot * K * W + c;  // this channel's column of the slot
   float S = mine[(size_t)(K - 1) * W];
+  for (int k = 0; k < index; ++k) {  // through the chunks before this one
+    const float2 ab = carry[(size_t)(blockIdx.y - index + k) * W + c];
+    S = ab.x * S + ab.y;
+  }
   const int blk = c / block_width, j = c - blk * block_width;
   const float* g = gates + (size_t)blk * 2 * block_width + j;  // + t * 2W: recurrence gate; + block_width: input gate
   const float br = bias_r[c], bi = bias_i[c], by = bias_y[c];
@@ -94,9 +147,10 @@ __global__ void recurrence_scan_kernel(const T* __restrict__ proj, const T* __re
       out[(size_t)(t + k) * W + c] = from_float<T>(S * y);
     }
   }
+  if (index != count - 1) return;  // the portion's last chunk leaves the state behind
   mine[(size_t)(K - 1) * W] = S;
   // the convolution's inputs at the last K-1 positions: from this portion where it reaches, else shifted up
-  const int n = t1 - t0;
+  const int n = item_start[item + 1] - item_start[item];
   float keep[MAX_TAPS];
   const float bx = bias_x[c];
 #pragma unroll
@@ -132,18 +186,26 @@ PSB_API int psb_causal_conv(const void* proj, int dtype, const void* bias_x, con
 
 PSB_API int psb_recurrence_scan(const void* proj, const void* u, int dtype, const void* gates, const void* bias_y,
                                 const void* bias_x, const void* bias_r, const void* bias_i, const void* lam, void* state,
-                                const void* item_start, const void* slots, void* out, int items, int W, int K, int blocks,
-                                int num_slots, float decay, cudaStream_t stream) {
-  if (items < 0 || W < 1 || K < 1 || K > MAX_TAPS || blocks < 1 || W % blocks || num_slots < 1)
-    PSB_REFUSE("recurrence_scan: bad sizes items=%d W=%d taps=%d blocks=%d", items, W, K, blocks);
-  if (items == 0) return 0;
-  if (items > 65535) PSB_REFUSE("recurrence_scan: %d requests in one step are too many for this kernel", items);
+                                const void* item_start, const void* slots, void* carry, void* out, int items, int T, int W,
+                                int K, int blocks, int num_slots, int chunk, float decay, cudaStream_t stream) {
+  if (items < 0 || T < 0 || W < 1 || K < 1 || K > MAX_TAPS || blocks < 1 || W % blocks || num_slots < 1 || chunk < 1)
+    PSB_REFUSE("recurrence_scan: bad sizes items=%d W=%d taps=%d blocks=%d chunk=%d", items, W, K, blocks, chunk);
+  if (items == 0 || T == 0) return 0;
+  const int chunks = T / chunk + items;  // at least the number of chunks of any cutting of T tokens into ``items`` portions
+  if (chunks > 65535) PSB_REFUSE("recurrence_scan: %d chunks in one step are too many for this kernel", chunks);
+  if (chunk < T && !carry) PSB_REFUSE("recurrence_scan: portions cut into chunks need the carry buffer");
   const int threads = 64;
+  const dim3 grid((W + threads - 1) / threads, chunks);
   PSB_DISPATCH_DTYPE(dtype, T_, {
-    psb_launch(recurrence_scan_kernel<T_>, dim3((W + threads - 1) / threads, items), dim3(threads), 0, stream,
-               (const T_*)proj, (const T_*)u, (const float*)gates, (const float*)bias_y, (const float*)bias_x,
-               (const float*)bias_r, (const float*)bias_i, (const float*)lam, (float*)state, (const int32_t*)item_start,
-               (const int32_t*)slots, (T_*)out, W, K, W / blocks, num_slots, decay);
+    if (chunk < T) {
+      psb_launch(recurrence_chunk_kernel<T_>, grid, dim3(threads), 0, stream, (const T_*)u, (const float*)gates,
+                 (const float*)bias_r, (const float*)bias_i, (const float*)lam, (const int32_t*)item_start, (float2*)carry,
+                 items, W, W / blocks, chunk, decay);
+    }
+    psb_launch(recurrence_scan_kernel<T_>, grid, dim3(threads), 0, stream, (const T_*)proj, (const T_*)u,
+               (const float*)gates, (const float*)bias_y, (const float*)bias_x, (const float*)bias_r, (const float*)bias_i,
+               (const float*)lam, (float*)state, (const int32_t*)item_start, (const int32_t*)slots, (const float2*)carry,
+               (T_*)out, items, W, K, W / blocks, num_slots, chunk, decay);
   });
   PSB_LAUNCH_CHECK("recurrence_scan");
   return 0;

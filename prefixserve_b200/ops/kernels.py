@@ -406,6 +406,9 @@ def step_prepare(records: torch.Tensor | None, kv_len: torch.Tensor | None, slot
                                  width, b, num_slots, _stream()), "step_prepare")
 
 
+PER_HEAD_LIBRARY_ROWS = 128  # per-head products of bfloat16 rows: from this many rows on, the library's batched product
+
+
 def linear_per_head(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,
                     out_dtype: torch.dtype | None = None) -> torch.Tensor:
     """out[t, h, :] = w[h] @ a[t, h, :] for a [T, heads, K] (a view whose last axis is contiguous and whose head axis
@@ -420,6 +423,13 @@ def linear_per_head(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None =
         out = torch.empty((t, heads, n), dtype=out_dtype or a.dtype, device=a.device)
     if tuple(out.shape) != (t, heads, n) or out.stride(2) != 1 or not out.is_cuda:
         raise KernelError(f"per-head product output must be [{t}, {heads}, {n}] with a contiguous last axis")
+    if t >= PER_HEAD_LIBRARY_ROWS and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+        # many rows: the library's batched product on the tensor cores (as ``linear`` sends its mid-sized products
+        # there), sums in float32 when the output is
+        y = torch.bmm(a.transpose(0, 1), w.transpose(1, 2), out_dtype=torch.float32) if out.dtype == torch.float32 \
+            else torch.bmm(a.transpose(0, 1), w.transpose(1, 2))
+        out.copy_(y.transpose(0, 1))
+        return out
     check(lib().psb_gemm_nt_batched(a.data_ptr(), _code(a, "left operand"), w.data_ptr(), _code(w, "weight"), out.data_ptr(),
                                     _code(out, "product"), t, n, k, a.stride(0), k, out.stride(0), heads, a.stride(1),
                                     n * k, out.stride(1), _stream()), "gemm_nt_batched")
@@ -560,6 +570,9 @@ def latent_attention(q_lat: torch.Tensor, cache: torch.Tensor, table: torch.Tens
     return out
 
 
+SCAN_CHUNK = 64  # tokens of a chunk when the recurrence cuts long portions into chunks that run side by side
+
+
 def causal_conv(proj: torch.Tensor, bias_x: torch.Tensor, conv_w: torch.Tensor, conv_b: torch.Tensor, state: torch.Tensor,
                 ctx) -> torch.Tensor:
     """proj [T, 2W] (gate branch, convolution branch): u[t] = conv over the branch's last K inputs (+ biases), inputs from
@@ -597,9 +610,12 @@ def recurrence_scan(proj: torch.Tensor, u: torch.Tensor, gates: torch.Tensor, bi
         if x.dtype != torch.float32 or x.numel() != w or not x.is_cuda or not x.is_contiguous():
             raise KernelError(f"{what} must be float32 [{w}] on the device")
     out = torch.empty((t, w), dtype=proj.dtype, device=proj.device)
+    # portions of more than a few chunks run their chunks side by side (two passes); short ones in one piece
+    chunk = SCAN_CHUNK if ctx.max_new_tokens > 2 * SCAN_CHUNK else max(t, 1)
+    carry = torch.empty((t // chunk + ctx.num_items, w, 2), dtype=torch.float32, device=proj.device) if chunk < t else None
     check(lib().psb_recurrence_scan(proj.data_ptr(), u.data_ptr(), _code(proj, "projection output"), gates.data_ptr(),
                                     bias_y.data_ptr(), bias_x.data_ptr(), bias_r.data_ptr(), bias_i.data_ptr(), lam.data_ptr(),
                                     state.data_ptr(), _i32(ctx.item_start, "item offsets").data_ptr(),
-                                    _i32(ctx.slots, "slots").data_ptr(), out.data_ptr(), ctx.num_items, w, k, blocks,
-                                    state.shape[0], float(decay), _stream()), "recurrence_scan")
+                                    _i32(ctx.slots, "slots").data_ptr(), _ptr(carry), out.data_ptr(), ctx.num_items, t, w, k,
+                                    blocks, state.shape[0], chunk, float(decay), _stream()), "recurrence_scan")
     return out

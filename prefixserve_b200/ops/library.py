@@ -139,9 +139,9 @@ _SIGNATURES: dict[str, list] = {
     "psb_latent_attention_max_rank": [],
     # (proj, dtype, bias_x, conv_w, conv_b, state, positions, token_item, item_start, slots, u_out, T, W, K, num_slots, stream)
     "psb_causal_conv": [P, I, P, P, P, P, P, P, P, P, P, I, I, I, I, P],
-    # (proj, u, dtype, gates, bias_y, bias_x, bias_r, bias_i, lam, state, item_start, slots, out, items, W, K, blocks,
-    #  num_slots, decay, stream)
-    "psb_recurrence_scan": [P, P, I, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, F, P],
+    # (proj, u, dtype, gates, bias_y, bias_x, bias_r, bias_i, lam, state, item_start, slots, carry, out, items, T, W, K, blocks,
+    #  num_slots, chunk, decay, stream)
+    "psb_recurrence_scan": [P, P, I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P],
     "psb_recurrence_max_taps": [],
 }
 
