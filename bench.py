@@ -835,9 +835,19 @@ def run_nerenex(args) -> dict:
                         cache.advance(it.slot, it.start + 1)
 
                 def kernels_of(fn) -> dict:
-                    with profile(activities=[ProfilerActivity.CUDA]) as prof:
-                        fn()
-                        torch.cuda.synchronize()
+                    # launched one after the other (no programmatic dependent launch, no replayed capture): a kernel
+                    # that starts early and waits for its predecessor would be charged the predecessor's time
+                    from prefixserve_b200.ops import library
+                    was_pdl, was_graphs = library.pdl_enabled(), runner.use_graphs
+                    library.set_pdl(False)
+                    runner.use_graphs = False
+                    try:
+                        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                            fn()
+                            torch.cuda.synchronize()
+                    finally:
+                        library.set_pdl(was_pdl)
+                        runner.use_graphs = was_graphs
                     rows: dict[str, list] = {}
                     for e in prof.events():
                         if e.device_type.name == "CUDA" and e.device_time_total > 0 and not e.name.startswith("Memcpy") \

@@ -74,6 +74,48 @@ gemm_nt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TC* __restric
   }
 }
 
+// Few rows (decode) against many small matrices: a warp per output column of one product, its lanes along K (the
+// weight row is read side by side), the product's rows of A in shared memory, the sums joined by a butterfly.
+constexpr int FEW_ROWS = 16;
+constexpr int FEW_WARPS = 8;
+
+template <typename TA, typename TW, typename TC>
+__global__ void __launch_bounds__(FEW_WARPS * 32)
+gemm_nt_few_rows_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TC* __restrict__ C, int M, int N, int K,
+                        int64_t lda, int64_t ldw, int64_t ldc, int64_t batch_a, int64_t batch_w, int64_t batch_c) {
+  extern __shared__ float rows_of_a[];  // [M][K]
+  pdl_trigger();
+  pdl_wait();
+  A += (size_t)blockIdx.y * batch_a;
+  W += (size_t)blockIdx.y * batch_w;
+  C += (size_t)blockIdx.y * batch_c;
+  for (int idx = threadIdx.x; idx < M * K; idx += blockDim.x) {
+    const int m = idx / K, k = idx - m * K;
+    rows_of_a[idx] = to_float<TA>(A[(size_t)m * lda + k]);
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * FEW_WARPS + warp;
+  if (n >= N) return;
+  const TW* wrow = W + (size_t)n * ldw;
+  float acc[FEW_ROWS];
+#pragma unroll
+  for (int m = 0; m < FEW_ROWS; ++m) acc[m] = 0.f;
+  for (int k = lane; k < K; k += 32) {
+    const float w = to_float<TW>(wrow[k]);
+#pragma unroll
+    for (int m = 0; m < FEW_ROWS; ++m)
+      if (m < M) acc[m] = fmaf(rows_of_a[m * K + k], w, acc[m]);
+  }
+#pragma unroll
+  for (int m = 0; m < FEW_ROWS; ++m) {
+    if (m < M) {
+      const float v = warp_sum(acc[m]);
+      if (lane == 0) C[(size_t)m * ldc + n] = from_float<TC>(v);
+    }
+  }
+}
+
 template <typename TA, typename TW>
 int launch_c(const void* a, const void* w, void* c, int c_dtype, int M, int N, int K, int64_t lda, int64_t ldw,
              int64_t ldc, int accumulate, cudaStream_t stream, int batch = 1, int64_t batch_a = 0, int64_t batch_w = 0,
@@ -114,6 +156,20 @@ PSB_API int psb_gemm_nt_batched(const void* a, int a_dtype, const void* w, int w
   if (lda < K || ldw < K || ldc < N) PSB_REFUSE("gemm_nt_batched: a leading dimension is smaller than its row");
   if (M == 0) return 0;
   int rc = 0;
+  if (M <= FEW_ROWS && (size_t)M * K * sizeof(float) <= 48 * 1024) {
+    const dim3 grid((N + FEW_WARPS - 1) / FEW_WARPS, batch);
+    const size_t smem = (size_t)M * K * sizeof(float);
+    PSB_DISPATCH_DTYPE(a_dtype, TA, {
+      PSB_DISPATCH_DTYPE(w_dtype, TW, {
+        PSB_DISPATCH_DTYPE(c_dtype, TC, {
+          psb_launch(gemm_nt_few_rows_kernel<TA, TW, TC>, grid, dim3(FEW_WARPS * 32), smem, stream, (const TA*)a, (const TW*)w,
+                     (TC*)c, M, N, K, lda, ldw, ldc, batch_a, batch_w, batch_c);
+        });
+      });
+    });
+    PSB_LAUNCH_CHECK("gemm_nt_batched");
+    return 0;
+  }
   PSB_DISPATCH_DTYPE(a_dtype, TA, {
     PSB_DISPATCH_DTYPE(w_dtype, TW, {
       rc = launch_c<TA, TW>(a, w, c, c_dtype, M, N, K, lda, ldw, ldc, 0, stream, batch, batch_a, batch_w, batch_c);

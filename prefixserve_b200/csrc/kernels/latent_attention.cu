@@ -268,6 +268,299 @@ latent_attention_kernel(const float* __restrict__ q_lat, const TKV* __restrict__
   }
 }
 
+// The same attention for bfloat16 rows whose sizes are multiples of eight (the usual case): a warp takes four keys at
+// a time and reads each row once, 16 bytes a lane, side by side (lane l holds elements 8l..8l+7, 8(l+32).., of the row
+// and of the query); the four scores are finished by a butterfly over the warp, and the weighted sum is accumulated
+// from the very registers the scores were computed from.  A block is one (token, head); its eight warps take the
+// groups of four keys in turn, counted from the first visible key, and are joined in warp order at the end.
+constexpr int ROW_WARPS = 8;
+constexpr int GROUP = 4;
+
+template <typename TO, int NP>
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+latent_attention_rows_kernel(const float* __restrict__ q_lat, const __nv_bfloat16* __restrict__ cache,
+                             const int32_t* __restrict__ table, int table_width, const int32_t* __restrict__ positions,
+                             const int32_t* __restrict__ token_item, const float* __restrict__ gate, TO* __restrict__ out,
+                             int heads, int rank, int rot, int page_size, int num_pages, int window, float scale) {
+  extern __shared__ __align__(16) float smem[];
+  pdl_trigger();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int D = rank + rot, pieces = D >> 3, value_pieces = rank >> 3;
+  float* part_ml = smem;                     // [ROW_WARPS][2]
+  float* part_o = smem + 2 * ROW_WARPS;      // [ROW_WARPS][rank]
+  const int t = blockIdx.x / heads, h = blockIdx.x - t * heads;
+  const int p = positions[t];
+  const int32_t* pages = table + (size_t)token_item[t] * table_width;
+  const float* qrow = q_lat + ((size_t)t * heads + h) * D;
+  float q[NP][8];
+#pragma unroll
+  for (int i = 0; i < NP; ++i) {
+    const int c = lane + 32 * i;
+    if (c < pieces) {
+      const float4 a = *reinterpret_cast<const float4*>(qrow + 8 * c), b = *reinterpret_cast<const float4*>(qrow + 8 * c + 4);
+      q[i][0] = a.x * scale; q[i][1] = a.y * scale; q[i][2] = a.z * scale; q[i][3] = a.w * scale;
+      q[i][4] = b.x * scale; q[i][5] = b.y * scale; q[i][6] = b.z * scale; q[i][7] = b.w * scale;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) q[i][e] = 0.f;
+    }
+  }
+  const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+  const int nkeys = p - lo + 1;
+  float m = -FLT_MAX, l = 0.f;
+  float acc[NP][8];
+#pragma unroll
+  for (int i = 0; i < NP; ++i)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[i][e] = 0.f;
+
+  for (int g = warp * GROUP; g < nkeys; g += ROW_WARPS * GROUP) {
+    uint4 r[GROUP][NP];
+    bool live[GROUP];
+#pragma unroll
+    for (int k = 0; k < GROUP; ++k) {
+      const int key = lo + g + k;
+      live[k] = g + k < nkeys;
+      const __nv_bfloat16* row = nullptr;
+      if (live[k]) {
+        const int page = pages[key / page_size];
+        live[k] = page >= 0 && page < num_pages;
+        if (live[k]) row = cache + ((size_t)page * page_size + (key % page_size)) * D;
+      }
+#pragma unroll
+      for (int i = 0; i < NP; ++i) {
+        const int c = lane + 32 * i;
+        r[k][i] = (live[k] && c < pieces) ? *reinterpret_cast<const uint4*>(row + 8 * c) : make_uint4(0, 0, 0, 0);
+      }
+    }
+    float s[GROUP];
+#pragma unroll
+    for (int k = 0; k < GROUP; ++k) {
+      float dot = 0.f;
+#pragma unroll
+      for (int i = 0; i < NP; ++i) {
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&r[k][i]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h2[e]);
+          dot = fmaf(q[i][2 * e], f.x, dot);
+          dot = fmaf(q[i][2 * e + 1], f.y, dot);
+        }
+      }
+      s[k] = dot;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+      for (int k = 0; k < GROUP; ++k) s[k] += __shfl_xor_sync(0xffffffffu, s[k], o);
+    float m_new = m;
+#pragma unroll
+    for (int k = 0; k < GROUP; ++k) m_new = live[k] ? fmaxf(m_new, s[k]) : m_new;
+    const float alpha = expf(m - m_new);
+    float pk[GROUP], add = 0.f;
+#pragma unroll
+    for (int k = 0; k < GROUP; ++k) {
+      pk[k] = live[k] ? expf(s[k] - m_new) : 0.f;
+      add += pk[k];
+    }
+    l = l * alpha + add;
+    m = m_new;
+#pragma unroll
+    for (int i = 0; i < NP; ++i) {
+      if (lane + 32 * i < value_pieces) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[i][e] *= alpha;
+#pragma unroll
+        for (int k = 0; k < GROUP; ++k) {
+          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&r[k][i]);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(h2[e]);
+            acc[i][2 * e] = fmaf(pk[k], f.x, acc[i][2 * e]);
+            acc[i][2 * e + 1] = fmaf(pk[k], f.y, acc[i][2 * e + 1]);
+          }
+        }
+      }
+    }
+  }
+  if (lane == 0) {
+    part_ml[2 * warp] = m;
+    part_ml[2 * warp + 1] = l;
+  }
+#pragma unroll
+  for (int i = 0; i < NP; ++i) {
+    const int c = lane + 32 * i;
+    if (c < value_pieces) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) part_o[(size_t)warp * rank + 8 * c + e] = acc[i][e];
+    }
+  }
+  __syncthreads();
+  float m_all = -FLT_MAX;
+#pragma unroll
+  for (int w = 0; w < ROW_WARPS; ++w) m_all = fmaxf(m_all, part_ml[2 * w]);
+  float f[ROW_WARPS], l_all = 0.f;
+#pragma unroll
+  for (int w = 0; w < ROW_WARPS; ++w) {
+    f[w] = part_ml[2 * w + 1] > 0.f ? expf(part_ml[2 * w] - m_all) : 0.f;
+    l_all += part_ml[2 * w + 1] * f[w];
+  }
+  const float wgt = (gate ? gate[(size_t)t * heads + h] : 1.f) / l_all;
+  TO* orow = out + ((size_t)t * heads + h) * rank;
+  for (int d = threadIdx.x; d < rank; d += blockDim.x) {
+    float v = 0.f;
+#pragma unroll
+    for (int w = 0; w < ROW_WARPS; ++w) v += part_o[(size_t)w * rank + d] * f[w];
+    orow[d] = from_float<TO>(v * wgt);
+  }
+}
+
+// ---- long portions: the band of keys a run of consecutive tokens can see, as matrix products -----------------------
+// A run of n consecutive tokens of one request, the first at position p0, sees keys p0 - window + 1 .. p0 + n - 1:
+// a band of window + n - 1 rows whatever p0 is.  The rows are gathered from the pages into one matrix (rows before the
+// sequence's start are zero and masked), the scores of all (token, head) rows against the band and the weighted
+// sums are products on the tensor cores (the library's), and the softmax between them is done here in float32.
+// The latent-space query enters its product as bfloat16, like any projection's result; the attention weights enter
+// theirs as pairs (hi | lo) of bfloat16 with hi + lo equal to the float32 weight to 16 bits, against the value rows
+// stacked twice, so that the weights are not cut to 8 bits on the way.
+
+template <typename TKV>
+__global__ void latent_band_gather_kernel(const TKV* __restrict__ cache, const int32_t* __restrict__ table, int table_width,
+                                          const int32_t* __restrict__ positions, const int32_t* __restrict__ token_item,
+                                          TKV* __restrict__ band, TKV* __restrict__ values2, int t0, int n, int KP, int D,
+                                          int rank, int page_size, int num_pages, int window) {
+  pdl_trigger();
+  pdl_wait();
+  const int j = blockIdx.x;
+  const int p0 = positions[t0];
+  const int kp = p0 - window + 1 + j;
+  TKV* dst = band + (size_t)j * D;
+  TKV* v1 = values2 + (size_t)j * rank;          // the value part once more, twice: rows j and KP + j of [2 KP, rank],
+  TKV* v2 = values2 + (size_t)(KP + j) * rank;   // the other operand of the weights' (hi | lo) pairs
+  const TKV* src = nullptr;
+  if (kp >= 0 && kp <= p0 + n - 1) {
+    const int page = table[(size_t)token_item[t0] * table_width + kp / page_size];
+    if (page >= 0 && page < num_pages) src = cache + ((size_t)page * page_size + (kp % page_size)) * D;
+  }
+  if (D % 8 == 0 && rank % 8 == 0 && sizeof(TKV) == 2) {
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    for (int d = threadIdx.x; d < D / 8; d += blockDim.x) {
+      const uint4 v = src ? reinterpret_cast<const uint4*>(src)[d] : zero;
+      reinterpret_cast<uint4*>(dst)[d] = v;
+      if (d < rank / 8) {
+        reinterpret_cast<uint4*>(v1)[d] = v;
+        reinterpret_cast<uint4*>(v2)[d] = v;
+      }
+    }
+  } else {
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+      const TKV v = src ? src[d] : from_float<TKV>(0.f);
+      dst[d] = v;
+      if (d < rank) {
+        v1[d] = v;
+        v2[d] = v;
+      }
+    }
+  }
+}
+
+__global__ void split_pairs_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo,
+                                   size_t total) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const float v = x[i];
+    const __nv_bfloat16 h = __float2bfloat16_rn(v);
+    hi[i] = h;
+    if (lo) lo[i] = __float2bfloat16_rn(v - __bfloat162float(h));
+  }
+}
+
+// One block per (token, head) row of the score matrix [rows, KP]; writes the softmax weights as (hi | lo) pairs into
+// [rows, 2 KP], zero where the key is not visible.  A thread keeps its scores in registers between the passes (up to
+// PER each; longer rows are read again).
+constexpr int BAND_PER = 16;
+
+__global__ void __launch_bounds__(128)
+latent_band_softmax_kernel(const float* __restrict__ scores, const int32_t* __restrict__ positions,
+                           __nv_bfloat16* __restrict__ weights, int t0, int heads, int KP, int window, float scale) {
+  __shared__ float scratch[8];
+  pdl_trigger();
+  pdl_wait();
+  const size_t row = blockIdx.x;
+  const int t = t0 + (int)(row / heads);
+  const int p0 = positions[t0], p = positions[t];
+  // column j holds key p0 - window + 1 + j; the row sees keys max(0, p - window + 1) .. p
+  const int first = max(0, p - window + 1) - (p0 - window + 1), last = p - (p0 - window + 1);
+  const float* a = scores + row * KP;
+  const bool held = KP <= BAND_PER * 128;
+  float v[BAND_PER];
+  float m = -FLT_MAX;
+  if (held) {
+#pragma unroll
+    for (int i = 0; i < BAND_PER; ++i) {
+      const int j = threadIdx.x + 128 * i;
+      v[i] = (j >= first && j <= last) ? a[j] * scale : -FLT_MAX;
+      m = fmaxf(m, v[i]);
+    }
+  } else {
+    for (int j = first + threadIdx.x; j <= last; j += blockDim.x) m = fmaxf(m, a[j] * scale);
+  }
+  m = warp_max(m);
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = m;
+  __syncthreads();
+  m = fmaxf(fmaxf(scratch[0], scratch[1]), fmaxf(scratch[2], scratch[3]));
+  __syncthreads();
+  float l = 0.f;
+  if (held) {
+#pragma unroll
+    for (int i = 0; i < BAND_PER; ++i) {
+      v[i] = v[i] > -FLT_MAX ? expf(v[i] - m) : 0.f;
+      l += v[i];
+    }
+  } else {
+    for (int j = first + threadIdx.x; j <= last; j += blockDim.x) l += expf(a[j] * scale - m);
+  }
+  l = warp_sum(l);
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = l;
+  __syncthreads();
+  l = (scratch[0] + scratch[1]) + (scratch[2] + scratch[3]);
+  const float inv = 1.f / l;
+  __nv_bfloat16* hi = weights + row * 2 * KP;
+  __nv_bfloat16* lo = hi + KP;
+  if (held) {
+#pragma unroll
+    for (int i = 0; i < BAND_PER; ++i) {
+      const int j = threadIdx.x + 128 * i;
+      if (j < KP) {
+        const float w = v[i] * inv;
+        const __nv_bfloat16 h = __float2bfloat16_rn(w);
+        hi[j] = h;
+        lo[j] = __float2bfloat16_rn(w - __bfloat162float(h));
+      }
+    }
+  } else {
+    for (int j = threadIdx.x; j < KP; j += blockDim.x) {
+      const float w = (j >= first && j <= last) ? expf(a[j] * scale - m) * inv : 0.f;
+      const __nv_bfloat16 h = __float2bfloat16_rn(w);
+      hi[j] = h;
+      lo[j] = __float2bfloat16_rn(w - __bfloat162float(h));
+    }
+  }
+}
+
+template <typename TO>
+__global__ void latent_band_finish_kernel(const float* __restrict__ o, const float* __restrict__ gate, TO* __restrict__ out,
+                                          int rank, size_t total) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const float g = gate ? gate[i / rank] : 1.f;
+    out[i] = from_float<TO>(o[i] * g);
+  }
+}
+
 }  // namespace
 
 PSB_API int psb_latent_prepare(const void* proj, int dtype, const void* positions, const void* token_item, const void* table,
@@ -322,6 +615,21 @@ PSB_API int psb_latent_attention(const void* q_lat, const void* cache, int cache
   const long long blocks = (long long)T * heads;
   if (blocks > 0x7fffffffLL) PSB_REFUSE("latent_attention: batch too large");
   if ((uintptr_t)cache & 15) PSB_REFUSE("latent_attention: the cache entry must be 16-byte aligned");
+  if (cache_dtype == PSB_BF16 && rank % 8 == 0 && rot % 8 == 0 && rank + rot <= 1024 && ((uintptr_t)q_lat & 15) == 0) {
+    const size_t bytes = (2 * ROW_WARPS + (size_t)ROW_WARPS * rank) * sizeof(float);
+    const int np = (rank + rot + 255) / 256;
+#define LATENT_ROWS(NP)                                                                                                  \
+    PSB_DISPATCH_DTYPE(out_dtype, TO, {                                                                                  \
+      psb_launch(latent_attention_rows_kernel<TO, NP>, dim3((unsigned)blocks), dim3(ROW_WARPS * 32), bytes, stream,     \
+                 (const float*)q_lat, (const __nv_bfloat16*)cache, (const int32_t*)table, table_width,                  \
+                 (const int32_t*)positions, (const int32_t*)token_item, (const float*)gate, (TO*)out, heads, rank, rot, \
+                 page_size, num_pages, window, scale);                                                                   \
+    })
+    if (np == 1) { LATENT_ROWS(1); } else if (np == 2) { LATENT_ROWS(2); } else if (np == 3) { LATENT_ROWS(3); } else { LATENT_ROWS(4); }
+#undef LATENT_ROWS
+    PSB_LAUNCH_CHECK("latent_attention");
+    return 0;
+  }
   const size_t smem = ((size_t)((rank + rot + 3) & ~3) + 2 * WARPS + (size_t)WARPS * rank) * sizeof(float);
 #define LATENT_LAUNCH(NACC)                                                                                              \
   PSB_DISPATCH_DTYPE(cache_dtype, TKV, {                                                                                 \
@@ -338,5 +646,55 @@ PSB_API int psb_latent_attention(const void* q_lat, const void* cache, int cache
   else { LATENT_LAUNCH(16); }
 #undef LATENT_LAUNCH
   PSB_LAUNCH_CHECK("latent_attention");
+  return 0;
+}
+
+// The band of keys that tokens t0 .. t0+n-1 (one request, consecutive) can see: ``band`` [KP, D] (KP >= window + n - 1)
+// and its value part twice over, ``values2`` [2 KP, rank].
+PSB_API int psb_latent_band_gather(const void* cache, int dtype, const void* table, int table_width, const void* positions,
+                                   const void* token_item, void* band, void* values2, int t0, int n, int KP, int D, int rank,
+                                   int page_size, int num_pages, int window, cudaStream_t stream) {
+  if (t0 < 0 || n < 1 || window < 1 || KP < window + n - 1 || D < 1 || rank < 1 || rank > D || page_size < 1 || num_pages < 1 || table_width < 1)
+    PSB_REFUSE("latent_band_gather: bad sizes t0=%d n=%d window=%d rows=%d D=%d rank=%d", t0, n, window, KP, D, rank);
+  if (((uintptr_t)cache | (uintptr_t)band | (uintptr_t)values2) & 15) PSB_REFUSE("latent_band_gather: cache and band must be 16-byte aligned");
+  PSB_DISPATCH_DTYPE(dtype, TKV, {
+    psb_launch(latent_band_gather_kernel<TKV>, dim3(KP), dim3(64), 0, stream, (const TKV*)cache, (const int32_t*)table,
+               table_width, (const int32_t*)positions, (const int32_t*)token_item, (TKV*)band, (TKV*)values2, t0, n, KP, D, rank,
+               page_size, num_pages, window);
+  });
+  PSB_LAUNCH_CHECK("latent_band_gather");
+  return 0;
+}
+
+// float32 -> bfloat16 (hi) and, if asked for, the bfloat16 nearest to what that rounding lost (lo)
+PSB_API int psb_split_pairs(const void* x, void* hi, void* lo, long long total, cudaStream_t stream) {
+  if (total < 0) PSB_REFUSE("split_pairs: negative size");
+  if (total == 0) return 0;
+  const long long blocks = (total + 255) / 256;
+  psb_launch(split_pairs_kernel, dim3((unsigned)(blocks > 148 * 32 ? 148 * 32 : blocks)), dim3(256), 0, stream, (const float*)x,
+             (__nv_bfloat16*)hi, (__nv_bfloat16*)lo, (size_t)total);
+  PSB_LAUNCH_CHECK("split_pairs");
+  return 0;
+}
+
+PSB_API int psb_latent_band_softmax(const void* scores, const void* positions, void* weights, int t0, int n, int heads, int KP,
+                                    int window, float scale, cudaStream_t stream) {
+  if (t0 < 0 || n < 1 || heads < 1 || window < 1 || KP < window + n - 1) PSB_REFUSE("latent_band_softmax: bad sizes");
+  psb_launch(latent_band_softmax_kernel, dim3((unsigned)((long long)n * heads)), dim3(128), 0, stream, (const float*)scores,
+             (const int32_t*)positions, (__nv_bfloat16*)weights, t0, heads, KP, window, scale);
+  PSB_LAUNCH_CHECK("latent_band_softmax");
+  return 0;
+}
+
+PSB_API int psb_latent_band_finish(const void* o, const void* gate, void* out, int out_dtype, int rank, long long total,
+                                   cudaStream_t stream) {
+  if (total < 0 || rank < 1) PSB_REFUSE("latent_band_finish: bad sizes");
+  if (total == 0) return 0;
+  const long long blocks = (total + 255) / 256;
+  PSB_DISPATCH_DTYPE(out_dtype, TO, {
+    psb_launch(latent_band_finish_kernel<TO>, dim3((unsigned)(blocks > 148 * 32 ? 148 * 32 : blocks)), dim3(256), 0, stream,
+               (const float*)o, (const float*)gate, (TO*)out, rank, (size_t)total);
+  });
+  PSB_LAUNCH_CHECK("latent_band_finish");
   return 0;
 }

@@ -41,7 +41,7 @@ __global__ void causal_conv_kernel(const T* __restrict__ proj, const float* __re
   int slot = slots[item];
   slot = slot < 0 ? 0 : (slot >= num_slots ? num_slots - 1 : slot);
   const float* tail = state + (size_t)slot * K * W;
-  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < W; c += gridDim.y * blockDim.x) {
     float acc = conv_b[c];
     for (int k = 0; k < K; ++k) {
       const int src = p - (K - 1) + k;  // position of the input under tap k
@@ -91,11 +91,24 @@ __global__ void recurrence_chunk_kernel(const T* __restrict__ u, const float* __
   const float br = bias_r[c], bi = bias_i[c];
   const float rate = decay * softplusf_(lam[c]);
   float A = 1.f, B = 0.f;
-  for (int t = t0; t < t1; ++t) {
-    const float r = sigmoidf_(g[(size_t)t * 2 * W] + br), i = sigmoidf_(g[(size_t)t * 2 * W + block_width] + bi);
-    const float a = expf(-rate * r);
-    B = a * B + sqrtf(1.f - a * a) * (i * to_float<T>(u[(size_t)t * W + c]));
-    A *= a;
+  constexpr int UNROLL = 8;
+  for (int t = t0; t < t1; t += UNROLL) {
+    float gr[UNROLL], gi[UNROLL], uu[UNROLL];
+#pragma unroll
+    for (int k = 0; k < UNROLL; ++k) {  // the loads of several tokens in flight together
+      const int tt = t + k < t1 ? t + k : t1 - 1;
+      gr[k] = g[(size_t)tt * 2 * W];
+      gi[k] = g[(size_t)tt * 2 * W + block_width];
+      uu[k] = to_float<T>(u[(size_t)tt * W + c]);
+    }
+#pragma unroll
+    for (int k = 0; k < UNROLL; ++k) {
+      if (t + k >= t1) break;
+      const float r = sigmoidf_(gr[k] + br), i = sigmoidf_(gi[k] + bi);
+      const float a = expf(-rate * r);
+      B = a * B + sqrtf(1.f - a * a) * (i * uu[k]);
+      A *= a;
+    }
   }
   carry[(size_t)blockIdx.y * W + c] = make_float2(A, B);
 }
@@ -126,7 +139,7 @@ __global__ void recurrence_scan_kernel(const T* __restrict__ proj, const T* __re
   const float* g = gates + (size_t)blk * 2 * block_width + j;  // + t * 2W: recurrence gate; + block_width: input gate
   const float br = bias_r[c], bi = bias_i[c], by = bias_y[c];
   const float rate = decay * softplusf_(lam[c]);
-  constexpr int UNROLL = 4;
+  constexpr int UNROLL = 8;
   for (int t = t0; t < t1; t += UNROLL) {
     float gr[UNROLL], gi[UNROLL], uu[UNROLL], yy[UNROLL];
 #pragma unroll
@@ -176,7 +189,7 @@ PSB_API int psb_causal_conv(const void* proj, int dtype, const void* bias_x, con
   if (T < 0 || W < 1 || K < 1 || K > MAX_TAPS || num_slots < 1) PSB_REFUSE("causal_conv: bad sizes T=%d W=%d taps=%d (at most %d)", T, W, K, MAX_TAPS);
   if (T == 0) return 0;
   PSB_DISPATCH_DTYPE(dtype, T_, {
-    psb_launch(causal_conv_kernel<T_>, dim3(T), dim3(W >= 1024 ? 256 : 128), 0, stream, (const T_*)proj, (const float*)bias_x,
+    psb_launch(causal_conv_kernel<T_>, dim3(T, (W + 127) / 128), dim3(128), 0, stream, (const T_*)proj, (const float*)bias_x,
                (const float*)conv_w, (const float*)conv_b, (const float*)state, (const int32_t*)positions,
                (const int32_t*)token_item, (const int32_t*)item_start, (const int32_t*)slots, (T_*)u_out, W, K, num_slots);
   });

@@ -406,6 +406,7 @@ def step_prepare(records: torch.Tensor | None, kv_len: torch.Tensor | None, slot
                                  width, b, num_slots, _stream()), "step_prepare")
 
 
+_BMM_INTO_VIEW = True   # cleared if this torch refuses ``out=`` with a result type of its own
 PER_HEAD_LIBRARY_ROWS = 128  # per-head products of bfloat16 rows: from this many rows on, the library's batched product
 
 
@@ -426,6 +427,18 @@ def linear_per_head(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None =
     if t >= PER_HEAD_LIBRARY_ROWS and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
         # many rows: the library's batched product on the tensor cores (as ``linear`` sends its mid-sized products
         # there), sums in float32 when the output is
+        global _BMM_INTO_VIEW
+        if _BMM_INTO_VIEW:  # straight into out's [heads, T, N] view: the library takes a leading dimension and a batch stride
+            try:
+                if out.dtype == torch.float32:
+                    torch.bmm(a.transpose(0, 1), w.transpose(1, 2), out_dtype=torch.float32, out=out.transpose(0, 1))
+                else:
+                    torch.bmm(a.transpose(0, 1), w.transpose(1, 2), out=out.transpose(0, 1))
+                return out
+            except (TypeError, RuntimeError):
+                if torch.cuda.is_current_stream_capturing():
+                    raise
+                _BMM_INTO_VIEW = False
         y = torch.bmm(a.transpose(0, 1), w.transpose(1, 2), out_dtype=torch.float32) if out.dtype == torch.float32 \
             else torch.bmm(a.transpose(0, 1), w.transpose(1, 2))
         out.copy_(y.transpose(0, 1))
@@ -550,11 +563,21 @@ def latent_query_rotate(q: torch.Tensor, positions: torch.Tensor, cos: torch.Ten
           "latent_query_rotate")
 
 
+BAND_MIN_TOKENS = 64    # portions from this many tokens on take the banded form of latent attention (bfloat16, with a window)
+BAND_CHUNK = 256        # tokens of a portion whose band of keys is handled by one set of products
+BAND_MAX_WINDOW = 8192  # wider windows stay with the kernel that walks the keys
+
+
 def latent_attention(q_lat: torch.Tensor, cache: torch.Tensor, table: torch.Tensor, positions: torch.Tensor,
                      token_item: torch.Tensor, gate: torch.Tensor | None, *, rank: int, page_size: int, window: int | None,
-                     scale: float, out_dtype: torch.dtype) -> torch.Tensor:
+                     scale: float, out_dtype: torch.dtype, items=None) -> torch.Tensor:
     """Softmax attention of latent-space queries [T, heads, rank + rot] (float32) over the cached rows
-    [pages, page_size, rank + rot]; returns sum_j p_j c_j times the head's gate, [T, heads, rank]."""
+    [pages, page_size, rank + rot]; returns sum_j p_j c_j times the head's gate, [T, heads, rank].
+
+    ``items`` (the step's host-side item list): portions of ``BAND_MIN_TOKENS`` tokens or more of a bfloat16 cache with
+    a window go through the banded form (the keys a run of tokens can see gathered into a matrix, scores and weighted
+    sums as products on the tensor cores, softmax in float32 between them); single tokens and short portions through
+    the kernel that walks the keys.  Which form a token takes depends on its portion's length only."""
     _dev(q_lat, "latent queries"), _dev(cache, "cache entry")
     _i32(table, "page table"), _i32(positions, "positions"), _i32(token_item, "token-to-item map")
     t, heads, d = q_lat.shape
@@ -563,11 +586,55 @@ def latent_attention(q_lat: torch.Tensor, cache: torch.Tensor, table: torch.Tens
     if gate is not None and (gate.dtype != torch.float32 or tuple(gate.shape) != (t, heads) or not gate.is_cuda):
         raise KernelError(f"head gates must be float32 [{t}, {heads}]")
     out = torch.empty((t, heads, rank), dtype=out_dtype, device=q_lat.device)
+    banded = []
+    if (items is not None and window and window <= BAND_MAX_WINDOW and cache.dtype == torch.bfloat16 and d % 8 == 0
+            and rank % 8 == 0):
+        banded = [(it.first_token, it.end - it.start) for it in items if it.end - it.start >= BAND_MIN_TOKENS]
+    at = 0
+    for first, n in banded + [(t, 0)]:   # the tokens between the banded portions: runs for the kernel that walks the keys
+        if first > at:
+            _latent_attention_walk(q_lat[at:first], cache, table, positions[at:first], token_item[at:first],
+                                   None if gate is None else gate[at:first], out[at:first], rank, page_size, window, scale)
+        at = first + n
+    if banded:
+        q16 = torch.empty((t, heads, d), dtype=torch.bfloat16, device=q_lat.device)
+        lo_t, hi_t = banded[0][0], banded[-1][0] + banded[-1][1]
+        check(lib().psb_split_pairs(q_lat[lo_t:hi_t].data_ptr(), q16[lo_t:hi_t].data_ptr(), None,
+                                    (hi_t - lo_t) * heads * d, _stream()), "split_pairs")
+        for first, n in banded:
+            for c0 in range(first, first + n, BAND_CHUNK):
+                _latent_attention_band(q16, cache, table, positions, token_item, gate, out, c0, min(BAND_CHUNK, first + n - c0),
+                                       rank, page_size, window, scale)
+    return out
+
+
+def _latent_attention_walk(q_lat, cache, table, positions, token_item, gate, out, rank, page_size, window, scale) -> None:
+    t, heads, d = q_lat.shape
     check(lib().psb_latent_attention(q_lat.data_ptr(), cache.data_ptr(), _code(cache, "cache entry"), table.data_ptr(), table.shape[1],
                                      positions.data_ptr(), token_item.data_ptr(), _ptr(gate), out.data_ptr(), _code(out, "output"),
                                      t, heads, rank, d - rank, page_size, cache.shape[0], int(window or 0), float(scale), _stream()),
           "latent_attention")
-    return out
+
+
+def _latent_attention_band(q16, cache, table, positions, token_item, gate, out, t0, n, rank, page_size, window, scale) -> None:
+    """Tokens t0 .. t0+n-1 (consecutive tokens of one request) against the window + n - 1 keys they can see."""
+    _, heads, d = q16.shape
+    kp = -(-(window + n - 1) // 8) * 8
+    dev = q16.device
+    band = torch.empty((kp, d), dtype=cache.dtype, device=dev)
+    values2 = torch.empty((2 * kp, rank), dtype=cache.dtype, device=dev)
+    check(lib().psb_latent_band_gather(cache.data_ptr(), _code(cache, "cache entry"), table.data_ptr(), table.shape[1],
+                                       positions.data_ptr(), token_item.data_ptr(), band.data_ptr(), values2.data_ptr(), t0, n, kp,
+                                       d, rank, page_size, cache.shape[0], window, _stream()), "latent_band_gather")
+    rows = n * heads
+    scores = torch.mm(q16[t0:t0 + n].view(rows, d), band.t(), out_dtype=torch.float32)
+    weights = torch.empty((rows, 2 * kp), dtype=torch.bfloat16, device=dev)
+    check(lib().psb_latent_band_softmax(scores.data_ptr(), positions.data_ptr(), weights.data_ptr(), t0, n, heads, kp, window,
+                                        float(scale), _stream()), "latent_band_softmax")
+    mixed = torch.mm(weights, values2, out_dtype=torch.float32)
+    check(lib().psb_latent_band_finish(mixed.data_ptr(), None if gate is None else gate[t0:t0 + n].data_ptr(),
+                                       out[t0:t0 + n].data_ptr(), _code(out, "output"), rank, rows * rank, _stream()),
+          "latent_band_finish")
 
 
 SCAN_CHUNK = 64  # tokens of a chunk when the recurrence cuts long portions into chunks that run side by side

@@ -137,6 +137,14 @@ _SIGNATURES: dict[str, list] = {
     #  page_size, num_pages, window, scale, stream)
     "psb_latent_attention": [P, P, I, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
     "psb_latent_attention_max_rank": [],
+    # (cache, dtype, table, table_width, positions, token_item, band, values2, t0, n, KP, D, rank, page_size, num_pages, window, stream)
+    "psb_latent_band_gather": [P, I, P, I, P, P, P, P, I, I, I, I, I, I, I, I, P],
+    # (x float32, hi, lo, total, stream)
+    "psb_split_pairs": [P, P, P, L, P],
+    # (scores, positions, weights [rows, 2 KP], t0, n, heads, KP, window, scale, stream)
+    "psb_latent_band_softmax": [P, P, P, I, I, I, I, I, F, P],
+    # (o, gate, out, out_dtype, rank, total, stream)
+    "psb_latent_band_finish": [P, P, P, I, I, L, P],
     # (proj, dtype, bias_x, conv_w, conv_b, state, positions, token_item, item_start, slots, u_out, T, W, K, num_slots, stream)
     "psb_causal_conv": [P, I, P, P, P, P, P, P, P, P, P, I, I, I, I, P],
     # (proj, u, dtype, gates, bias_y, bias_x, bias_r, bias_i, lam, state, item_start, slots, carry, out, items, T, W, K, blocks,

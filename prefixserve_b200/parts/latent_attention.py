@@ -103,7 +103,8 @@ class LatentAttention(Mixer):
         ops.latent_query_rotate(q, ctx.positions, self.position.cos, self.position.sin, q_lat, heads=heads, plain=self.dim,
                                 rot=self.rot, rot_dims=self.rot_dims, rank=self.rank)
         mixed = ops.latent_attention(q_lat, cache.kv, table, ctx.positions, ctx.token_item, gate if self.head_gate else None, rank=self.rank,
-                                     page_size=cache.page_size, window=self.window, scale=self.scale, out_dtype=x.dtype)
+                                     page_size=cache.page_size, window=self.window, scale=self.scale, out_dtype=x.dtype,
+                                     items=ctx.items)
         values = ops.linear_per_head(mixed, self.w_uv)
         return ops.linear(values.view(t, heads * self.vdim), self.w_o)
 
