@@ -576,7 +576,7 @@ PSB_API int psb_latent_prepare(const void* proj, int dtype, const void* position
   if (T == 0) return 0;
   PSB_DISPATCH_DTYPE(dtype, T_, {
     PSB_DISPATCH_DTYPE(cache_dtype, TKV, {
-      psb_launch(latent_prepare_kernel<T_, TKV>, dim3(T), dim3(128), 0, stream, (const T_*)proj, (const int32_t*)positions,
+      psb_launch(latent_prepare_kernel<T_, TKV>, dim3(T), dim3(q_rank + rank >= 1024 ? 512 : 128), 0, stream, (const T_*)proj, (const int32_t*)positions,
                  (const int32_t*)token_item, (const int32_t*)table, table_width, (const float*)cos_t, (const float*)sin_t,
                  (const float*)gain_q, (const float*)gain_kv, (T_*)cq_out, (float*)gate_out, (TKV*)cache, q_rank, rank, rot,
                  rot_dims, heads, page_size, num_pages, max_positions, eps);

@@ -26,28 +26,42 @@ constexpr int MAX_TAPS = 16;
 __device__ __forceinline__ float softplusf_(float x) { return log1pf(expf(-fabsf(x))) + fmaxf(x, 0.f); }
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-x)); }
 
+constexpr int CONV_TOKENS = 8;  // tokens a block of the convolution handles: their look-ups are in flight together
+
 template <typename T>
 __global__ void causal_conv_kernel(const T* __restrict__ proj, const float* __restrict__ bias_x,
                                    const float* __restrict__ conv_w, const float* __restrict__ conv_b,
                                    const float* __restrict__ state, const int32_t* __restrict__ positions,
                                    const int32_t* __restrict__ token_item, const int32_t* __restrict__ item_start,
-                                   const int32_t* __restrict__ slots, T* __restrict__ u_out, int W, int K, int num_slots) {
+                                   const int32_t* __restrict__ slots, T* __restrict__ u_out, int T_tokens, int W, int K,
+                                   int num_slots) {
   pdl_trigger();
   pdl_wait();
-  const int t = blockIdx.x;
-  const int item = token_item[t];
-  const int first = item_start[item];         // the portion's first token in the step
-  const int p = positions[t], p0 = positions[first];
-  int slot = slots[item];
-  slot = slot < 0 ? 0 : (slot >= num_slots ? num_slots - 1 : slot);
-  const float* tail = state + (size_t)slot * K * W;
-  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < W; c += gridDim.y * blockDim.x) {
-    float acc = conv_b[c];
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  const int tb = blockIdx.x * CONV_TOKENS;
+  int p[CONV_TOKENS], p0[CONV_TOKENS], slot[CONV_TOKENS];
+#pragma unroll
+  for (int i = 0; i < CONV_TOKENS; ++i) {
+    const int t = min(tb + i, T_tokens - 1);
+    const int item = token_item[t];
+    p[i] = positions[t];
+    p0[i] = positions[item_start[item]];  // position of the portion's first token in the step
+    const int s = slots[item];
+    slot[i] = s < 0 ? 0 : (s >= num_slots ? num_slots - 1 : s);
+  }
+  if (c >= W) return;
+  const float bx = bias_x[c], cb = conv_b[c];
+#pragma unroll
+  for (int i = 0; i < CONV_TOKENS; ++i) {
+    const int t = tb + i;
+    if (t >= T_tokens) break;
+    const float* tail = state + (size_t)slot[i] * K * W;
+    float acc = cb;
     for (int k = 0; k < K; ++k) {
-      const int src = p - (K - 1) + k;  // position of the input under tap k
+      const int src = p[i] - (K - 1) + k;  // position of the input under tap k
       float x = 0.f;
-      if (src >= p0) x = to_float<T>(from_float<T>(to_float<T>(proj[(size_t)(t - (p - src)) * 2 * W + W + c]) + bias_x[c]));
-      else if (src >= 0) x = tail[(size_t)(src - p0 + K - 1) * W + c];
+      if (src >= p0[i]) x = to_float<T>(from_float<T>(to_float<T>(proj[(size_t)(t - (p[i] - src)) * 2 * W + W + c]) + bx));
+      else if (src >= 0) x = tail[(size_t)(src - p0[i] + K - 1) * W + c];
       acc = fmaf(conv_w[(size_t)c * K + k], x, acc);
     }
     u_out[(size_t)t * W + c] = from_float<T>(acc);
@@ -189,9 +203,10 @@ PSB_API int psb_causal_conv(const void* proj, int dtype, const void* bias_x, con
   if (T < 0 || W < 1 || K < 1 || K > MAX_TAPS || num_slots < 1) PSB_REFUSE("causal_conv: bad sizes T=%d W=%d taps=%d (at most %d)", T, W, K, MAX_TAPS);
   if (T == 0) return 0;
   PSB_DISPATCH_DTYPE(dtype, T_, {
-    psb_launch(causal_conv_kernel<T_>, dim3(T, (W + 127) / 128), dim3(128), 0, stream, (const T_*)proj, (const float*)bias_x,
-               (const float*)conv_w, (const float*)conv_b, (const float*)state, (const int32_t*)positions,
-               (const int32_t*)token_item, (const int32_t*)item_start, (const int32_t*)slots, (T_*)u_out, W, K, num_slots);
+    psb_launch(causal_conv_kernel<T_>, dim3((T + CONV_TOKENS - 1) / CONV_TOKENS, (W + 127) / 128), dim3(128), 0, stream,
+               (const T_*)proj, (const float*)bias_x, (const float*)conv_w, (const float*)conv_b, (const float*)state,
+               (const int32_t*)positions, (const int32_t*)token_item, (const int32_t*)item_start, (const int32_t*)slots,
+               (T_*)u_out, T, W, K, num_slots);
   });
   PSB_LAUNCH_CHECK("causal_conv");
   return 0;
