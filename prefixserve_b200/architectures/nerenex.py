@@ -52,7 +52,8 @@ def nerenex_spec(cfg: NerenexConfig) -> ModelSpec:
         hidden_size=cfg.width,
         max_positions=MAX_POSITIONS,
         embedding=part("hashed_pair_embedding", vocab_size=cfg.vocab, hidden_size=cfg.width, buckets=cfg.bigram_buckets,
-                       mul_prev=cfg.bigram_mul_prev, mul_cur=cfg.bigram_mul_cur),
+                       mul_prev=cfg.bigram_mul_prev, mul_cur=cfg.bigram_mul_cur) if cfg.bigram_buckets is not None
+        else part("token_embedding", vocab_size=cfg.vocab, hidden_size=cfg.width),
         layers=tuple(layers),
         schedule=sequential_schedule(len(layers)),
         final_norm=norm,

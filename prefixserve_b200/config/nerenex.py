@@ -120,7 +120,7 @@ class NerenexConfig:
     width: int
     residual_mult: float
     norm_eps: float
-    bigram_buckets: int
+    bigram_buckets: int | None   # None: a config.json without embedding.bigram, the plain token embedding
     bigram_mul_prev: int
     bigram_mul_cur: int
     layers: tuple[NerenexLayer, ...]
@@ -132,7 +132,7 @@ class NerenexConfig:
     def from_dicts(raw: Mapping[str, Any], generation: Mapping[str, Any] | None = None) -> "NerenexConfig":
         if raw.get("architecture") != ARCHITECTURE and ARCHITECTURE not in (raw.get("architectures") or []):
             raise UnsupportedModelError(f"config.json does not describe a {ARCHITECTURE} model")
-        bigram = _need(_need(raw, "embedding", "the top level"), "bigram", "embedding")
+        bigram = (raw.get("embedding") or {}).get("bigram")
         layers = []
         for i, entry in enumerate(_need(raw, "layers", "the top level")):
             where = f"layers[{i}]"
@@ -158,22 +158,23 @@ class NerenexConfig:
             width=_positive(_need(raw, "width", "the top level"), "width"),
             residual_mult=float(_need(raw, "residual_mult", "the top level")),
             norm_eps=float(_need(_need(raw, "norm", "the top level"), "eps", "norm")),
-            bigram_buckets=_positive(_need(bigram, "buckets", "embedding.bigram"), "embedding.bigram.buckets"),
-            bigram_mul_prev=int(_need(bigram, "mul_prev", "embedding.bigram")),
-            bigram_mul_cur=int(_need(bigram, "mul_cur", "embedding.bigram")),
+            bigram_buckets=None if bigram is None else _positive(_need(bigram, "buckets", "embedding.bigram"), "embedding.bigram.buckets"),
+            bigram_mul_prev=0 if bigram is None else int(_need(bigram, "mul_prev", "embedding.bigram")),
+            bigram_mul_cur=0 if bigram is None else int(_need(bigram, "mul_cur", "embedding.bigram")),
             layers=tuple(layers),
             stop_token_ids=frozenset(stops),
         )
 
     def to_config_json(self) -> dict[str, Any]:
+        embedding = {} if self.bigram_buckets is None else {
+            "bigram": {"buckets": self.bigram_buckets, "mul_prev": self.bigram_mul_prev, "mul_cur": self.bigram_mul_cur}}
         return {
             "architecture": ARCHITECTURE,
             "vocab": self.vocab,
             "width": self.width,
             "residual_mult": self.residual_mult,
             "norm": {"eps": self.norm_eps},
-            "embedding": {"bigram": {"buckets": self.bigram_buckets, "mul_prev": self.bigram_mul_prev,
-                                     "mul_cur": self.bigram_mul_cur}},
+            "embedding": embedding,
             "layers": [{"type": layer.mixer.kind, "mixer": layer.mixer.to_dict(),
                         "mlp": None if layer.ff is None else {"kind": "dense", "ff": layer.ff}} for layer in self.layers],
         }

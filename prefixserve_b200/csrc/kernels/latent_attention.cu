@@ -271,12 +271,13 @@ latent_attention_kernel(const float* __restrict__ q_lat, const TKV* __restrict__
 // The same attention for bfloat16 rows whose sizes are multiples of eight (the usual case): a warp takes four keys at
 // a time and reads each row once, 16 bytes a lane, side by side (lane l holds elements 8l..8l+7, 8(l+32).., of the row
 // and of the query); the four scores are finished by a butterfly over the warp, and the weighted sum is accumulated
-// from the very registers the scores were computed from.  A block is one (token, head); its eight warps take the
-// groups of four keys in turn, counted from the first visible key, and are joined in warp order at the end.
+// from the very registers the scores were computed from.  A block is one token and one head or two (two where the
+// head count is even: both use every row the block loads); its eight warps take the groups of four keys in turn,
+// counted from the first visible key, and are joined in warp order at the end.
 constexpr int ROW_WARPS = 8;
 constexpr int GROUP = 4;
 
-template <typename TO, int NP>
+template <typename TO, int NP, int HP>
 __global__ void __launch_bounds__(ROW_WARPS * 32)
 latent_attention_rows_kernel(const float* __restrict__ q_lat, const __nv_bfloat16* __restrict__ cache,
                              const int32_t* __restrict__ table, int table_width, const int32_t* __restrict__ positions,
@@ -287,33 +288,42 @@ latent_attention_rows_kernel(const float* __restrict__ q_lat, const __nv_bfloat1
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int D = rank + rot, pieces = D >> 3, value_pieces = rank >> 3;
-  float* part_ml = smem;                     // [ROW_WARPS][2]
-  float* part_o = smem + 2 * ROW_WARPS;      // [ROW_WARPS][rank]
-  const int t = blockIdx.x / heads, h = blockIdx.x - t * heads;
+  float* part_ml = smem;                          // [HP][ROW_WARPS][2]
+  float* part_o = smem + 2 * ROW_WARPS * HP;      // [HP][ROW_WARPS][rank]
+  const int per_token = heads / HP;               // HP heads of a token share a block and every row it loads
+  const int t = blockIdx.x / per_token, h0 = (blockIdx.x - t * per_token) * HP;
   const int p = positions[t];
   const int32_t* pages = table + (size_t)token_item[t] * table_width;
-  const float* qrow = q_lat + ((size_t)t * heads + h) * D;
-  float q[NP][8];
+  float q[HP][NP][8];
 #pragma unroll
-  for (int i = 0; i < NP; ++i) {
-    const int c = lane + 32 * i;
-    if (c < pieces) {
-      const float4 a = *reinterpret_cast<const float4*>(qrow + 8 * c), b = *reinterpret_cast<const float4*>(qrow + 8 * c + 4);
-      q[i][0] = a.x * scale; q[i][1] = a.y * scale; q[i][2] = a.z * scale; q[i][3] = a.w * scale;
-      q[i][4] = b.x * scale; q[i][5] = b.y * scale; q[i][6] = b.z * scale; q[i][7] = b.w * scale;
-    } else {
+  for (int hh = 0; hh < HP; ++hh) {
+    const float* qrow = q_lat + ((size_t)t * heads + h0 + hh) * D;
 #pragma unroll
-      for (int e = 0; e < 8; ++e) q[i][e] = 0.f;
+    for (int i = 0; i < NP; ++i) {
+      const int c = lane + 32 * i;
+      if (c < pieces) {
+        const float4 a = *reinterpret_cast<const float4*>(qrow + 8 * c), b = *reinterpret_cast<const float4*>(qrow + 8 * c + 4);
+        q[hh][i][0] = a.x * scale; q[hh][i][1] = a.y * scale; q[hh][i][2] = a.z * scale; q[hh][i][3] = a.w * scale;
+        q[hh][i][4] = b.x * scale; q[hh][i][5] = b.y * scale; q[hh][i][6] = b.z * scale; q[hh][i][7] = b.w * scale;
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) q[hh][i][e] = 0.f;
+      }
     }
   }
   const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
   const int nkeys = p - lo + 1;
-  float m = -FLT_MAX, l = 0.f;
-  float acc[NP][8];
+  float m[HP], l[HP];
+  float acc[HP][NP][8];
 #pragma unroll
-  for (int i = 0; i < NP; ++i)
+  for (int hh = 0; hh < HP; ++hh) {
+    m[hh] = -FLT_MAX;
+    l[hh] = 0.f;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) acc[i][e] = 0.f;
+    for (int i = 0; i < NP; ++i)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[hh][i][e] = 0.f;
+  }
 
   for (int g = warp * GROUP; g < nkeys; g += ROW_WARPS * GROUP) {
     uint4 r[GROUP][NP];
@@ -334,85 +344,95 @@ latent_attention_rows_kernel(const float* __restrict__ q_lat, const __nv_bfloat1
         r[k][i] = (live[k] && c < pieces) ? *reinterpret_cast<const uint4*>(row + 8 * c) : make_uint4(0, 0, 0, 0);
       }
     }
-    float s[GROUP];
 #pragma unroll
-    for (int k = 0; k < GROUP; ++k) {
-      float dot = 0.f;
+    for (int hh = 0; hh < HP; ++hh) {
+      float s[GROUP];
 #pragma unroll
-      for (int i = 0; i < NP; ++i) {
-        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&r[k][i]);
+      for (int k = 0; k < GROUP; ++k) {
+        float dot = 0.f;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 f = __bfloat1622float2(h2[e]);
-          dot = fmaf(q[i][2 * e], f.x, dot);
-          dot = fmaf(q[i][2 * e + 1], f.y, dot);
-        }
-      }
-      s[k] = dot;
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-      for (int k = 0; k < GROUP; ++k) s[k] += __shfl_xor_sync(0xffffffffu, s[k], o);
-    float m_new = m;
-#pragma unroll
-    for (int k = 0; k < GROUP; ++k) m_new = live[k] ? fmaxf(m_new, s[k]) : m_new;
-    const float alpha = expf(m - m_new);
-    float pk[GROUP], add = 0.f;
-#pragma unroll
-    for (int k = 0; k < GROUP; ++k) {
-      pk[k] = live[k] ? expf(s[k] - m_new) : 0.f;
-      add += pk[k];
-    }
-    l = l * alpha + add;
-    m = m_new;
-#pragma unroll
-    for (int i = 0; i < NP; ++i) {
-      if (lane + 32 * i < value_pieces) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[i][e] *= alpha;
-#pragma unroll
-        for (int k = 0; k < GROUP; ++k) {
+        for (int i = 0; i < NP; ++i) {
           const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&r[k][i]);
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const float2 f = __bfloat1622float2(h2[e]);
-            acc[i][2 * e] = fmaf(pk[k], f.x, acc[i][2 * e]);
-            acc[i][2 * e + 1] = fmaf(pk[k], f.y, acc[i][2 * e + 1]);
+            dot = fmaf(q[hh][i][2 * e], f.x, dot);
+            dot = fmaf(q[hh][i][2 * e + 1], f.y, dot);
+          }
+        }
+        s[k] = dot;
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int k = 0; k < GROUP; ++k) s[k] += __shfl_xor_sync(0xffffffffu, s[k], o);
+      float m_new = m[hh];
+#pragma unroll
+      for (int k = 0; k < GROUP; ++k) m_new = live[k] ? fmaxf(m_new, s[k]) : m_new;
+      const float alpha = expf(m[hh] - m_new);
+      float pk[GROUP], add = 0.f;
+#pragma unroll
+      for (int k = 0; k < GROUP; ++k) {
+        pk[k] = live[k] ? expf(s[k] - m_new) : 0.f;
+        add += pk[k];
+      }
+      l[hh] = l[hh] * alpha + add;
+      m[hh] = m_new;
+#pragma unroll
+      for (int i = 0; i < NP; ++i) {
+        if (lane + 32 * i < value_pieces) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[hh][i][e] *= alpha;
+#pragma unroll
+          for (int k = 0; k < GROUP; ++k) {
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&r[k][i]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 f = __bfloat1622float2(h2[e]);
+              acc[hh][i][2 * e] = fmaf(pk[k], f.x, acc[hh][i][2 * e]);
+              acc[hh][i][2 * e + 1] = fmaf(pk[k], f.y, acc[hh][i][2 * e + 1]);
+            }
           }
         }
       }
     }
   }
-  if (lane == 0) {
-    part_ml[2 * warp] = m;
-    part_ml[2 * warp + 1] = l;
-  }
 #pragma unroll
-  for (int i = 0; i < NP; ++i) {
-    const int c = lane + 32 * i;
-    if (c < value_pieces) {
+  for (int hh = 0; hh < HP; ++hh) {
+    if (lane == 0) {
+      part_ml[2 * (hh * ROW_WARPS + warp)] = m[hh];
+      part_ml[2 * (hh * ROW_WARPS + warp) + 1] = l[hh];
+    }
 #pragma unroll
-      for (int e = 0; e < 8; ++e) part_o[(size_t)warp * rank + 8 * c + e] = acc[i][e];
+    for (int i = 0; i < NP; ++i) {
+      const int c = lane + 32 * i;
+      if (c < value_pieces) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) part_o[((size_t)hh * ROW_WARPS + warp) * rank + 8 * c + e] = acc[hh][i][e];
+      }
     }
   }
   __syncthreads();
-  float m_all = -FLT_MAX;
 #pragma unroll
-  for (int w = 0; w < ROW_WARPS; ++w) m_all = fmaxf(m_all, part_ml[2 * w]);
-  float f[ROW_WARPS], l_all = 0.f;
+  for (int hh = 0; hh < HP; ++hh) {
+    const float* ml = part_ml + 2 * hh * ROW_WARPS;
+    float m_all = -FLT_MAX;
 #pragma unroll
-  for (int w = 0; w < ROW_WARPS; ++w) {
-    f[w] = part_ml[2 * w + 1] > 0.f ? expf(part_ml[2 * w] - m_all) : 0.f;
-    l_all += part_ml[2 * w + 1] * f[w];
-  }
-  const float wgt = (gate ? gate[(size_t)t * heads + h] : 1.f) / l_all;
-  TO* orow = out + ((size_t)t * heads + h) * rank;
-  for (int d = threadIdx.x; d < rank; d += blockDim.x) {
-    float v = 0.f;
+    for (int w = 0; w < ROW_WARPS; ++w) m_all = fmaxf(m_all, ml[2 * w]);
+    float f[ROW_WARPS], l_all = 0.f;
 #pragma unroll
-    for (int w = 0; w < ROW_WARPS; ++w) v += part_o[(size_t)w * rank + d] * f[w];
-    orow[d] = from_float<TO>(v * wgt);
+    for (int w = 0; w < ROW_WARPS; ++w) {
+      f[w] = ml[2 * w + 1] > 0.f ? expf(ml[2 * w] - m_all) : 0.f;
+      l_all += ml[2 * w + 1] * f[w];
+    }
+    const float wgt = (gate ? gate[(size_t)t * heads + h0 + hh] : 1.f) / l_all;
+    TO* orow = out + ((size_t)t * heads + h0 + hh) * rank;
+    for (int d = threadIdx.x; d < rank; d += blockDim.x) {
+      float v = 0.f;
+#pragma unroll
+      for (int w = 0; w < ROW_WARPS; ++w) v += part_o[((size_t)hh * ROW_WARPS + w) * rank + d] * f[w];
+      orow[d] = from_float<TO>(v * wgt);
+    }
   }
 }
 
@@ -616,16 +636,32 @@ PSB_API int psb_latent_attention(const void* q_lat, const void* cache, int cache
   if (blocks > 0x7fffffffLL) PSB_REFUSE("latent_attention: batch too large");
   if ((uintptr_t)cache & 15) PSB_REFUSE("latent_attention: the cache entry must be 16-byte aligned");
   if (cache_dtype == PSB_BF16 && rank % 8 == 0 && rot % 8 == 0 && rank + rot <= 1024 && ((uintptr_t)q_lat & 15) == 0) {
-    const size_t bytes = (2 * ROW_WARPS + (size_t)ROW_WARPS * rank) * sizeof(float);
+    // two heads of a token share a block (and every row it loads) where the head count is even and registers allow
+    const int hp = (heads % 2 == 0 && rank + rot <= 768) ? 2 : 1;
+    const size_t bytes = (size_t)hp * (2 * ROW_WARPS + (size_t)ROW_WARPS * rank) * sizeof(float);
     const int np = (rank + rot + 255) / 256;
-#define LATENT_ROWS(NP)                                                                                                  \
-    PSB_DISPATCH_DTYPE(out_dtype, TO, {                                                                                  \
-      psb_launch(latent_attention_rows_kernel<TO, NP>, dim3((unsigned)blocks), dim3(ROW_WARPS * 32), bytes, stream,     \
-                 (const float*)q_lat, (const __nv_bfloat16*)cache, (const int32_t*)table, table_width,                  \
-                 (const int32_t*)positions, (const int32_t*)token_item, (const float*)gate, (TO*)out, heads, rank, rot, \
-                 page_size, num_pages, window, scale);                                                                   \
-    })
-    if (np == 1) { LATENT_ROWS(1); } else if (np == 2) { LATENT_ROWS(2); } else if (np == 3) { LATENT_ROWS(3); } else { LATENT_ROWS(4); }
+    const long long row_blocks = blocks / hp;
+#define LATENT_ROWS(NP, HP)                                                                                              \
+    do {                                                                                                                 \
+      static PsbPerDevice big;                                                                                           \
+      PSB_DISPATCH_DTYPE(out_dtype, TO, {                                                                                \
+        if (bytes > 48 * 1024 && !big.get()) {                                                                           \
+          if (cudaFuncSetAttribute(latent_attention_rows_kernel<TO, NP, HP>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                   96 * 1024) != cudaSuccess)                                                            \
+            PSB_REFUSE("latent_attention: cannot reserve %d bytes of shared memory", (int)bytes);                        \
+          big.set();                                                                                                     \
+        }                                                                                                                \
+        psb_launch(latent_attention_rows_kernel<TO, NP, HP>, dim3((unsigned)row_blocks), dim3(ROW_WARPS * 32), bytes,    \
+                   stream, (const float*)q_lat, (const __nv_bfloat16*)cache, (const int32_t*)table, table_width,         \
+                   (const int32_t*)positions, (const int32_t*)token_item, (const float*)gate, (TO*)out, heads, rank,     \
+                   rot, page_size, num_pages, window, scale);                                                            \
+      });                                                                                                                \
+    } while (0)
+    if (hp == 2) {
+      if (np == 1) LATENT_ROWS(1, 2); else if (np == 2) LATENT_ROWS(2, 2); else LATENT_ROWS(3, 2);
+    } else {
+      if (np == 1) LATENT_ROWS(1, 1); else if (np == 2) LATENT_ROWS(2, 1); else if (np == 3) LATENT_ROWS(3, 1); else LATENT_ROWS(4, 1);
+    }
 #undef LATENT_ROWS
     PSB_LAUNCH_CHECK("latent_attention");
     return 0;

@@ -26,9 +26,9 @@ constexpr int MAX_TAPS = 16;
 __device__ __forceinline__ float softplusf_(float x) { return log1pf(expf(-fabsf(x))) + fmaxf(x, 0.f); }
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-x)); }
 
-constexpr int CONV_TOKENS = 8;  // tokens a block of the convolution handles: their look-ups are in flight together
-
-template <typename T>
+// CONV_TOKENS: tokens a block of the convolution handles, their look-ups in flight together (8 for prompt portions,
+// 1 for a handful of decoded tokens, where the blocks are few as it is)
+template <typename T, int CONV_TOKENS>
 __global__ void causal_conv_kernel(const T* __restrict__ proj, const float* __restrict__ bias_x,
                                    const float* __restrict__ conv_w, const float* __restrict__ conv_b,
                                    const float* __restrict__ state, const int32_t* __restrict__ positions,
@@ -203,10 +203,17 @@ PSB_API int psb_causal_conv(const void* proj, int dtype, const void* bias_x, con
   if (T < 0 || W < 1 || K < 1 || K > MAX_TAPS || num_slots < 1) PSB_REFUSE("causal_conv: bad sizes T=%d W=%d taps=%d (at most %d)", T, W, K, MAX_TAPS);
   if (T == 0) return 0;
   PSB_DISPATCH_DTYPE(dtype, T_, {
-    psb_launch(causal_conv_kernel<T_>, dim3((T + CONV_TOKENS - 1) / CONV_TOKENS, (W + 127) / 128), dim3(128), 0, stream,
-               (const T_*)proj, (const float*)bias_x, (const float*)conv_w, (const float*)conv_b, (const float*)state,
-               (const int32_t*)positions, (const int32_t*)token_item, (const int32_t*)item_start, (const int32_t*)slots,
-               (T_*)u_out, T, W, K, num_slots);
+    if (T >= 256) {
+      psb_launch(causal_conv_kernel<T_, 8>, dim3((T + 7) / 8, (W + 127) / 128), dim3(128), 0, stream,
+                 (const T_*)proj, (const float*)bias_x, (const float*)conv_w, (const float*)conv_b, (const float*)state,
+                 (const int32_t*)positions, (const int32_t*)token_item, (const int32_t*)item_start, (const int32_t*)slots,
+                 (T_*)u_out, T, W, K, num_slots);
+    } else {
+      psb_launch(causal_conv_kernel<T_, 1>, dim3(T, (W + 127) / 128), dim3(128), 0, stream,
+                 (const T_*)proj, (const float*)bias_x, (const float*)conv_w, (const float*)conv_b, (const float*)state,
+                 (const int32_t*)positions, (const int32_t*)token_item, (const int32_t*)item_start, (const int32_t*)slots,
+                 (T_*)u_out, T, W, K, num_slots);
+    }
   });
   PSB_LAUNCH_CHECK("causal_conv");
   return 0;

@@ -51,6 +51,15 @@ def test_config_refusals_name_the_key(damage, word):
         NerenexConfig.from_dicts(raw)
 
 
+def test_without_a_pair_table_the_embedding_is_the_plain_one():
+    raw = copy.deepcopy(nm.CONFIGS["rec_only"])
+    raw["embedding"] = {}
+    arch = architecture_of(raw)
+    model = build_model(arch.to_spec(arch.read_config(raw, None)))
+    names = {arch.tensor_name(path) for path in model.param_table()}
+    assert "bigram" not in names and "embed" in names and len(model.cache_needs()) == 1
+
+
 def test_recurrence_blocks_must_divide_the_channels():
     raw = copy.deepcopy(nm.CONFIGS["rec_only"])
     raw["layers"][0]["mixer"]["blocks"] = 7
