@@ -282,12 +282,14 @@ __global__ void __launch_bounds__(ROW_WARPS * 32)
 latent_attention_rows_kernel(const float* __restrict__ q_lat, const __nv_bfloat16* __restrict__ cache,
                              const int32_t* __restrict__ table, int table_width, const int32_t* __restrict__ positions,
                              const int32_t* __restrict__ token_item, const float* __restrict__ gate, TO* __restrict__ out,
-                             int heads, int rank, int rot, int page_size, int num_pages, int window, float scale) {
+                             float* __restrict__ partial, int heads, int rank, int rot, int page_size, int num_pages,
+                             int window, float scale) {
   extern __shared__ __align__(16) float smem[];
   pdl_trigger();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int D = rank + rot, pieces = D >> 3, value_pieces = rank >> 3;
+  const int splits = gridDim.y, split = blockIdx.y;  // several blocks may share a (token, heads): each takes every splits-th turn
   float* part_ml = smem;                          // [HP][ROW_WARPS][2]
   float* part_o = smem + 2 * ROW_WARPS * HP;      // [HP][ROW_WARPS][rank]
   const int per_token = heads / HP;               // HP heads of a token share a block and every row it loads
@@ -325,7 +327,7 @@ latent_attention_rows_kernel(const float* __restrict__ q_lat, const __nv_bfloat1
       for (int e = 0; e < 8; ++e) acc[hh][i][e] = 0.f;
   }
 
-  for (int g = warp * GROUP; g < nkeys; g += ROW_WARPS * GROUP) {
+  for (int g = (split * ROW_WARPS + warp) * GROUP; g < nkeys; g += splits * ROW_WARPS * GROUP) {
     uint4 r[GROUP][NP];
     bool live[GROUP];
 #pragma unroll
@@ -425,6 +427,20 @@ latent_attention_rows_kernel(const float* __restrict__ q_lat, const __nv_bfloat1
       f[w] = ml[2 * w + 1] > 0.f ? expf(ml[2 * w] - m_all) : 0.f;
       l_all += ml[2 * w + 1] * f[w];
     }
+    if (splits > 1) {  // this block's share: maximum, sum and the weighted sum as it stands; the merge kernel joins the shares
+      float* mine = partial + (((size_t)t * heads + h0 + hh) * splits + split) * (rank + 2);
+      if (threadIdx.x == 0) {
+        mine[0] = m_all;
+        mine[1] = l_all;
+      }
+      for (int d = threadIdx.x; d < rank; d += blockDim.x) {
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < ROW_WARPS; ++w) v += part_o[((size_t)hh * ROW_WARPS + w) * rank + d] * f[w];
+        mine[2 + d] = v;
+      }
+      continue;
+    }
     const float wgt = (gate ? gate[(size_t)t * heads + h0 + hh] : 1.f) / l_all;
     TO* orow = out + ((size_t)t * heads + h0 + hh) * rank;
     for (int d = threadIdx.x; d < rank; d += blockDim.x) {
@@ -433,6 +449,38 @@ latent_attention_rows_kernel(const float* __restrict__ q_lat, const __nv_bfloat1
       for (int w = 0; w < ROW_WARPS; ++w) v += part_o[((size_t)hh * ROW_WARPS + w) * rank + d] * f[w];
       orow[d] = from_float<TO>(v * wgt);
     }
+  }
+}
+
+// Joins the shares of the blocks that split a (token, head)'s keys among them, in split order.
+constexpr int MAX_SPLITS = 8;
+
+template <typename TO>
+__global__ void latent_attention_merge_kernel(const float* __restrict__ partial, const float* __restrict__ gate,
+                                              TO* __restrict__ out, int rank, int splits) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t unit = blockIdx.x;  // token * heads + head
+  const float* mine = partial + unit * splits * (rank + 2);
+  float m_all = -FLT_MAX;
+  for (int s = 0; s < splits; ++s) m_all = fmaxf(m_all, mine[(size_t)s * (rank + 2)]);
+  float f[MAX_SPLITS], l_all = 0.f;
+#pragma unroll
+  for (int s = 0; s < MAX_SPLITS; ++s) {
+    f[s] = 0.f;
+    if (s < splits) {
+      const float l = mine[(size_t)s * (rank + 2) + 1];
+      f[s] = l > 0.f ? expf(mine[(size_t)s * (rank + 2)] - m_all) : 0.f;
+      l_all += l * f[s];
+    }
+  }
+  const float wgt = (gate ? gate[unit] : 1.f) / l_all;
+  for (int d = threadIdx.x; d < rank; d += blockDim.x) {
+    float v = 0.f;
+#pragma unroll
+    for (int s = 0; s < MAX_SPLITS; ++s)
+      if (s < splits) v += mine[(size_t)s * (rank + 2) + 2 + d] * f[s];
+    out[unit * rank + d] = from_float<TO>(v * wgt);
   }
 }
 
@@ -623,10 +671,17 @@ PSB_API int psb_latent_query_rotate(const void* q, int dtype, const void* positi
 
 PSB_API int psb_latent_attention_max_rank() { return 1024; }
 
+// 1 if the kernel that reads four rows side by side takes the case (bfloat16 rows, sizes in multiples of eight)
+PSB_API int psb_latent_attention_rows_supported(int cache_dtype, int rank, int rot) {
+  return cache_dtype == PSB_BF16 && rank % 8 == 0 && rot % 8 == 0 && rank + rot <= 1024;
+}
+
+// ``heads_per_block`` (1 or 2) and ``splits`` (1..8 blocks sharing a (token, heads)'s keys, with ``partial``
+// float32 [T, heads, splits, rank + 2] as their meeting place) only matter where that kernel runs.
 PSB_API int psb_latent_attention(const void* q_lat, const void* cache, int cache_dtype, const void* table, int table_width,
                                  const void* positions, const void* token_item, const void* gate, void* out, int out_dtype,
                                  int T, int heads, int rank, int rot, int page_size, int num_pages, int window, float scale,
-                                 cudaStream_t stream) {
+                                 int heads_per_block, int splits, void* partial, cudaStream_t stream) {
   if (T < 0 || heads < 1 || rank < 1 || rot < 0) PSB_REFUSE("latent_attention: bad sizes T=%d heads=%d rank=%d rot=%d", T, heads, rank, rot);
   if (rank > 1024 || rank + rot > 2048) PSB_REFUSE("latent_attention: a latent of %d (+%d rotated) is beyond this kernel (1024, 2048 together)", rank, rot);
   if (page_size < 1 || num_pages < 1 || table_width < 1) PSB_REFUSE("latent_attention: bad paging (page_size=%d pages=%d width=%d)", page_size, num_pages, table_width);
@@ -635,9 +690,11 @@ PSB_API int psb_latent_attention(const void* q_lat, const void* cache, int cache
   const long long blocks = (long long)T * heads;
   if (blocks > 0x7fffffffLL) PSB_REFUSE("latent_attention: batch too large");
   if ((uintptr_t)cache & 15) PSB_REFUSE("latent_attention: the cache entry must be 16-byte aligned");
-  if (cache_dtype == PSB_BF16 && rank % 8 == 0 && rot % 8 == 0 && rank + rot <= 1024 && ((uintptr_t)q_lat & 15) == 0) {
-    // two heads of a token share a block (and every row it loads) where the head count is even and registers allow
-    const int hp = (heads % 2 == 0 && rank + rot <= 768) ? 2 : 1;
+  if (psb_latent_attention_rows_supported(cache_dtype, rank, rot) && ((uintptr_t)q_lat & 15) == 0) {
+    // two heads of a token may share a block (and every row it loads) where the head count is even and registers allow
+    const int hp = heads_per_block;
+    if (hp < 1 || hp > 2 || heads % hp || (hp == 2 && rank + rot > 768)) PSB_REFUSE("latent_attention: %d heads a block do not go with %d heads of %d", hp, heads, rank + rot);
+    if (splits < 1 || splits > MAX_SPLITS || (splits > 1 && !partial)) PSB_REFUSE("latent_attention: 1 to %d splits (with their scratch), not %d", MAX_SPLITS, splits);
     const size_t bytes = (size_t)hp * (2 * ROW_WARPS + (size_t)ROW_WARPS * rank) * sizeof(float);
     const int np = (rank + rot + 255) / 256;
     const long long row_blocks = blocks / hp;
@@ -651,10 +708,10 @@ PSB_API int psb_latent_attention(const void* q_lat, const void* cache, int cache
             PSB_REFUSE("latent_attention: cannot reserve %d bytes of shared memory", (int)bytes);                        \
           big.set();                                                                                                     \
         }                                                                                                                \
-        psb_launch(latent_attention_rows_kernel<TO, NP, HP>, dim3((unsigned)row_blocks), dim3(ROW_WARPS * 32), bytes,    \
-                   stream, (const float*)q_lat, (const __nv_bfloat16*)cache, (const int32_t*)table, table_width,         \
-                   (const int32_t*)positions, (const int32_t*)token_item, (const float*)gate, (TO*)out, heads, rank,     \
-                   rot, page_size, num_pages, window, scale);                                                            \
+        psb_launch(latent_attention_rows_kernel<TO, NP, HP>, dim3((unsigned)row_blocks, splits), dim3(ROW_WARPS * 32),   \
+                   bytes, stream, (const float*)q_lat, (const __nv_bfloat16*)cache, (const int32_t*)table, table_width,  \
+                   (const int32_t*)positions, (const int32_t*)token_item, (const float*)gate, (TO*)out, (float*)partial, \
+                   heads, rank, rot, page_size, num_pages, window, scale);                                               \
       });                                                                                                                \
     } while (0)
     if (hp == 2) {
@@ -664,6 +721,13 @@ PSB_API int psb_latent_attention(const void* q_lat, const void* cache, int cache
     }
 #undef LATENT_ROWS
     PSB_LAUNCH_CHECK("latent_attention");
+    if (splits > 1) {
+      PSB_DISPATCH_DTYPE(out_dtype, TO, {
+        psb_launch(latent_attention_merge_kernel<TO>, dim3((unsigned)blocks), dim3(128), 0, stream, (const float*)partial,
+                   (const float*)gate, (TO*)out, rank, splits);
+      });
+      PSB_LAUNCH_CHECK("latent_attention_merge");
+    }
     return 0;
   }
   const size_t smem = ((size_t)((rank + rot + 3) & ~3) + 2 * WARPS + (size_t)WARPS * rank) * sizeof(float);

@@ -570,7 +570,7 @@ BAND_MAX_WINDOW = 8192  # wider windows stay with the kernel that walks the keys
 
 def latent_attention(q_lat: torch.Tensor, cache: torch.Tensor, table: torch.Tensor, positions: torch.Tensor,
                      token_item: torch.Tensor, gate: torch.Tensor | None, *, rank: int, page_size: int, window: int | None,
-                     scale: float, out_dtype: torch.dtype, items=None) -> torch.Tensor:
+                     scale: float, out_dtype: torch.dtype, items=None, key_hint: int = 0) -> torch.Tensor:
     """Softmax attention of latent-space queries [T, heads, rank + rot] (float32) over the cached rows
     [pages, page_size, rank + rot]; returns sum_j p_j c_j times the head's gate, [T, heads, rank].
 
@@ -594,7 +594,8 @@ def latent_attention(q_lat: torch.Tensor, cache: torch.Tensor, table: torch.Tens
     for first, n in banded + [(t, 0)]:   # the tokens between the banded portions: runs for the kernel that walks the keys
         if first > at:
             _latent_attention_walk(q_lat[at:first], cache, table, positions[at:first], token_item[at:first],
-                                   None if gate is None else gate[at:first], out[at:first], rank, page_size, window, scale)
+                                   None if gate is None else gate[at:first], out[at:first], rank, page_size, window, scale,
+                                   key_hint=int(window or key_hint))
         at = first + n
     if banded:
         q16 = torch.empty((t, heads, d), dtype=torch.bfloat16, device=q_lat.device)
@@ -608,11 +609,28 @@ def latent_attention(q_lat: torch.Tensor, cache: torch.Tensor, table: torch.Tens
     return out
 
 
-def _latent_attention_walk(q_lat, cache, table, positions, token_item, gate, out, rank, page_size, window, scale) -> None:
+ROWS_BLOCKS_WANTED = 296   # blocks that keep every SM of a B200 busy with the kernel that reads rows side by side (two an SM)
+ROWS_KEYS_PER_SPLIT = 128  # no block of that kernel is given fewer keys than this by splitting
+
+
+def _latent_attention_walk(q_lat, cache, table, positions, token_item, gate, out, rank, page_size, window, scale,
+                           key_hint: int = 0) -> None:
+    """Tokens that walk their keys.  ``key_hint``: about how many keys the longest walk has (the window, or the step's
+    longest sequence), for the choice of how many blocks share a (token, head)."""
     t, heads, d = q_lat.shape
+    hp, splits, partial = 1, 1, None
+    if lib().psb_latent_attention_rows_supported(_code(cache, "cache entry"), rank, d - rank):
+        if heads % 2 == 0 and d <= 768:
+            hp = 2  # two heads of a token share a block and every row it loads
+        blocks = t * heads // hp
+        if blocks < ROWS_BLOCKS_WANTED and key_hint >= 2 * ROWS_KEYS_PER_SPLIT:
+            splits = max(1, min(8, -(-ROWS_BLOCKS_WANTED // blocks), key_hint // ROWS_KEYS_PER_SPLIT))
+        if splits > 1:
+            partial = torch.empty((t, heads, splits, rank + 2), dtype=torch.float32, device=q_lat.device)
     check(lib().psb_latent_attention(q_lat.data_ptr(), cache.data_ptr(), _code(cache, "cache entry"), table.data_ptr(), table.shape[1],
                                      positions.data_ptr(), token_item.data_ptr(), _ptr(gate), out.data_ptr(), _code(out, "output"),
-                                     t, heads, rank, d - rank, page_size, cache.shape[0], int(window or 0), float(scale), _stream()),
+                                     t, heads, rank, d - rank, page_size, cache.shape[0], int(window or 0), float(scale), hp, splits,
+                                     _ptr(partial), _stream()),
           "latent_attention")
 
 

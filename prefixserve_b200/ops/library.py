@@ -134,8 +134,10 @@ _SIGNATURES: dict[str, list] = {
     # (q, dtype, positions, cos, sin, q_lat, T, heads, plain, rot, rot_dims, rank, max_positions, stream)
     "psb_latent_query_rotate": [P, I, P, P, P, P, I, I, I, I, I, I, I, P],
     # (q_lat, cache, cache_dtype, table, table_width, positions, token_item, gate, out, out_dtype, T, heads, rank, rot,
-    #  page_size, num_pages, window, scale, stream)
-    "psb_latent_attention": [P, P, I, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
+    #  page_size, num_pages, window, scale, heads_per_block, splits, partial, stream)
+    "psb_latent_attention": [P, P, I, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P],
+    # (cache_dtype, rank, rot) -> 1 if the kernel that reads rows side by side takes the case
+    "psb_latent_attention_rows_supported": [I, I, I],
     "psb_latent_attention_max_rank": [],
     # (cache, dtype, table, table_width, positions, token_item, band, values2, t0, n, KP, D, rank, page_size, num_pages, window, stream)
     "psb_latent_band_gather": [P, I, P, I, P, P, P, P, I, I, I, I, I, I, I, I, P],

@@ -104,7 +104,7 @@ class LatentAttention(Mixer):
                                 rot=self.rot, rot_dims=self.rot_dims, rank=self.rank)
         mixed = ops.latent_attention(q_lat, cache.kv, table, ctx.positions, ctx.token_item, gate if self.head_gate else None, rank=self.rank,
                                      page_size=cache.page_size, window=self.window, scale=self.scale, out_dtype=x.dtype,
-                                     items=ctx.items)
+                                     items=ctx.items, key_hint=int(ctx.extras.get("static_kv_len") or ctx.max_kv_len))
         values = ops.linear_per_head(mixed, self.w_uv)
         return ops.linear(values.view(t, heads * self.vdim), self.w_o)
 

@@ -173,6 +173,25 @@ def test_a_loud_key_far_back_without_a_window(tmp_path, dtype):
         assert worst_error(rows, truth) < LIMIT[dtype]
 
 
+@pytest.mark.parametrize("window, heads", [(300, 2), (None, 3)])
+def test_single_tokens_whose_keys_several_blocks_share(tmp_path, window, heads):
+    """bfloat16 rows in multiples of eight with hundreds of visible keys: the blocks of a (token, head) split the keys
+    among them and a second kernel joins their shares; two heads share a block where the head count is even."""
+    cfg = nm.config([nm.layer("latent_attention", nm.attention(heads=heads, dim=16, rot_dim=8, vdim=16, q_rank=32, kv_rank=24,
+                                                                scale=0.3, window=window, base=1e4), 48)], vocab=96, width=64)
+    held, exact = stored(nm.tensors(cfg, seed=31), "bfloat16")
+    folder = nm.write_folder(tmp_path / "m", cfg, held)
+    seqs = {"a": helpers.random_tokens(96, 420, seed=8), "b": helpers.random_tokens(96, 150, seed=9)}
+    truth = {rid: plain.forward(cfg, exact, toks) for rid, toks in seqs.items()}
+    from prefixserve_b200.ops import library
+    before = library.launch_counts.copy()
+    rows = replay(folder, "bfloat16", helpers.trace_tail_decode(seqs, tail=100))
+    assert worst_error(rows, truth) < LIMIT["bfloat16"]
+    rows = replay(folder, "bfloat16", helpers.trace_mixed(seqs, max_live=2, seed=2))
+    assert worst_error(rows, truth) < LIMIT["bfloat16"]
+    assert (library.launch_counts - before)["latent_attention"] > 0
+
+
 def test_a_long_memory_survives_portions_and_decoding(tmp_path):
     """A recurrence that forgets slowly: a lost state or a lost convolution input at a portion's start shows for long."""
     cfg = nm.CONFIGS["rec_only"]
