@@ -259,6 +259,23 @@ def test_per_head_product_on_slices_of_wider_tensors():
     assert torch.allclose(out[:, :, :5].double(), want, atol=1e-5) and float(out[:, :, 5:].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("m", [1, 8, 9, 33, 64, 65, 127, 128, 300, 1100])
+def test_products_with_the_output_widths_this_design_brings(m):
+    """The fused input projections have output widths such as q_rank + kv_rank + rot_dim + heads, which are multiples
+    of nothing; every route of ``ops.linear`` (few rows, a few dozen, the tensor-core tiles, the library) takes them."""
+    from prefixserve_b200 import ops
+    g = torch.Generator().manual_seed(m)
+    for k, n in [(64, 6), (96, 294), (512, 1900), (512, 2047), (72, 100), (100, 37), (256, 4098)]:
+        x = torch.randn(m, k, generator=g).to(torch.bfloat16).cuda()
+        w = (torch.randn(n, k, generator=g) / k ** 0.5).to(torch.bfloat16).cuda()
+        got = ops.linear(x, w).float().cpu()
+        want = (x.double() @ w.double().T).cpu()
+        assert got.shape == (m, n)
+        assert float((got.double() - want).abs().max()) < 0.03 * max(1.0, float(want.abs().max())), (m, k, n)
+    from prefixserve_b200.ops import library
+    assert library.tcgen05_status() == 0
+
+
 # ---- generation through the scheduler --------------------------------------------------------------------------
 
 def greedy(cfg, exact, prompt, n):
