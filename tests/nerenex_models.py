@@ -22,7 +22,7 @@ def layer(kind, mixer, ff):
     return {"type": kind, "mixer": mixer, "mlp": None if ff is None else {"kind": "dense", "ff": ff}}
 
 
-def config(layers, vocab=61, width=24, mult=0.7, eps=1e-5, buckets=53, mul_prev=31, mul_cur=7):
+def config(layers, vocab=61, width=24, mult=0.8, eps=2e-5, buckets=53, mul_prev=31, mul_cur=7):
     return {"architecture": "Nerenex", "vocab": vocab, "width": width, "residual_mult": mult, "norm": {"eps": eps},
             "embedding": {"bigram": {"buckets": buckets, "mul_prev": mul_prev, "mul_cur": mul_cur}}, "layers": layers}
 
