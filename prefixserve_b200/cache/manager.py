@@ -1,9 +1,9 @@
 """The cache manager: pages of keys and values, page tables, request slots.
 
 Every cache entry of a model (one per writing mixer call) states a need:
-keys and values for all tokens, for a window of them, and/or a fixed-size
-state per request.  Entries whose paged need has the same window form a
-*group*; a group has a page pool of its own (ids, reference counts), one page
+keys and values for all tokens, for a window of them or for the current run
+of a chunked mask, and/or a fixed-size state per request.  Entries whose paged
+need has the same window and chunk form a *group*; a group has a page pool of its own (ids, reference counts), one page
 table row per request slot, and its entries' tensors are indexed by the same
 page id.  A request holds one slot; the slot indexes the page table rows and
 the fixed-state tensors.
@@ -54,6 +54,16 @@ class _Group:
     pool: BlockManager
     tables: SeqTables
     entries: list[int]
+    chunk: int | None = None  # keys before the current run of ``chunk`` positions are out of reach
+
+    def lowest_key(self, position: int) -> int:
+        """The lowest key position a query at ``position`` or later can still read."""
+        low = 0
+        if self.window is not None:
+            low = max(low, position - self.window + 1)
+        if self.chunk is not None:
+            low = max(low, position // self.chunk * self.chunk)
+        return low
 
 
 class CacheManager:
@@ -83,19 +93,19 @@ class CacheManager:
         # group entries by window
         self.groups: list[_Group] = []
         self.entry_group: list[int | None] = []
-        by_window: dict[int | None, int] = {}
+        by_window: dict[tuple[int | None, int | None], int] = {}
         for i, need in enumerate(self.needs):
             if need.paged is None:
                 self.entry_group.append(None)
                 continue
-            w = need.paged.window
-            if w is not None and w < 1:
-                raise ValueError(f"cache entry {i}: window {w} must be >= 1")
-            if w not in by_window:
-                by_window[w] = len(self.groups)
+            w, c = need.paged.window, need.paged.chunk
+            if (w is not None and w < 1) or (c is not None and c < 1):
+                raise ValueError(f"cache entry {i}: window {w} and chunk {c} must be >= 1")
+            if (w, c) not in by_window:
+                by_window[(w, c)] = len(self.groups)
                 n = num_pages[len(self.groups)] if isinstance(num_pages, Mapping) else int(num_pages)
-                self.groups.append(_Group(w, BlockManager(n), SeqTables(num_slots, self.max_pages_per_seq), []))
-            g = by_window[w]
+                self.groups.append(_Group(w, BlockManager(n), SeqTables(num_slots, self.max_pages_per_seq), [], c))
+            g = by_window[(w, c)]
             self.groups[g].entries.append(i)
             self.entry_group.append(g)
 
@@ -115,7 +125,8 @@ class CacheManager:
         self.resident_words = at
 
         has_state = any(n.state is not None for n in self.needs)
-        self.prefix_cache_possible = len(self.groups) == 1 and self.groups[0].window is None and not has_state
+        self.prefix_cache_possible = (len(self.groups) == 1 and self.groups[0].window is None
+                                      and self.groups[0].chunk is None and not has_state)
         self.tree: RadixTree | None = None
         if enable_prefix_cache and self.prefix_cache_possible:
             self.tree = RadixTree(self.groups[0].pool, page_size, hash_seed)
@@ -170,14 +181,23 @@ class CacheManager:
 
     @staticmethod
     def group_page_bytes(needs: Sequence[CacheNeed], page_size: int, dtype: torch.dtype) -> dict[int | None, int]:
-        """window (None: all keys) -> bytes one page id of that group costs over the group's entries, in the order
-        in which the groups are numbered (first appearance among the entries)."""
+        """reach -> bytes one page id of that group costs over the group's entries, in the order in which the groups are
+        numbered (first appearance among the entries).  The reach of a group is how far back its keys can be read: None
+        (all keys), a window, or ("chunk", size[, window]) for the runs of a chunked mask."""
         item = torch.empty((), dtype=dtype).element_size()
-        out: dict[int | None, int] = {}
+        out: dict = {}
         for n in needs:
             if n.paged is not None:
-                out[n.paged.window] = out.get(n.paged.window, 0) + n.paged.planes * n.paged.num_kv_heads * page_size * n.paged.head_dim * item
+                key = n.paged.window if n.paged.chunk is None else ("chunk", n.paged.chunk, n.paged.window)
+                out[key] = out.get(key, 0) + n.paged.planes * n.paged.num_kv_heads * page_size * n.paged.head_dim * item
         return out
+
+    @staticmethod
+    def reach_tokens(reach) -> int | None:
+        """The most keys a query of a group with this reach (a key of ``group_page_bytes``) can read; None: all."""
+        if isinstance(reach, tuple):
+            return min(x for x in reach[1:] if x is not None)
+        return reach
 
     def num_pages(self, group: int = 0) -> int:
         return self.groups[group].pool.num_blocks
@@ -253,10 +273,7 @@ class CacheManager:
     # ------------------------------------------------------------------ pages
     def _first_needed_page(self, g: _Group, upto_start: int) -> int:
         """Lowest page index a query at position >= upto_start can still read."""
-        if g.window is None:
-            return 0
-        lowest_key = max(0, upto_start - g.window + 1)
-        return lowest_key // self.page_size
+        return g.lowest_key(upto_start) // self.page_size
 
     def shortfall(self, slot: int, upto: int) -> dict[int, int]:
         """Pages still to take, per group, so that positions < upto are covered. {} when nothing is missing."""
@@ -302,7 +319,7 @@ class CacheManager:
         """Records that positions < computed are in the cache; window groups give back pages now out of reach."""
         self._position[slot] = computed
         for g in self.groups:
-            if g.window is None:
+            if g.window is None and g.chunk is None:
                 continue
             ids = g.tables.release_front(slot, self._first_needed_page(g, computed))
             if ids:

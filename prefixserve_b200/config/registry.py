@@ -32,6 +32,8 @@ class Architecture:
     tensor_name: Callable[[str], str]
     # tensors a checkpoint may carry that the model never reads
     ignorable: Callable[[Any, str], bool] = lambda cfg, name: False
+    # (typed config, model folder) -> typed config, for sizes that only the checkpoint's tensor shapes give
+    refine_config: Callable[[Any, Any], Any] | None = None
 
 
 _ARCHITECTURES: dict[str, Architecture] = {}
@@ -84,4 +86,7 @@ def read_model_folder(folder: str | Path) -> tuple[Architecture, Any]:
     gen_file = folder / "generation_config.json"
     gen = json.loads(gen_file.read_text()) if gen_file.exists() else None
     arch = architecture_of(raw)
-    return arch, arch.read_config(raw, gen)
+    config = arch.read_config(raw, gen)
+    if arch.refine_config is not None:
+        config = arch.refine_config(config, folder)
+    return arch, config

@@ -47,7 +47,7 @@ def part(kind: str, **params: Any) -> PartSpec:
 @dataclass(frozen=True)
 class LayerSpec:
     """One block: a mixer, a feed-forward and their norms, put together by the named arrangement
-    (``parts.block``: "pre_norm", "parallel", "gated_post_norm", or one registered there).  ``ffn`` and ``ffn_norm`` may be None: a
+    (``parts.block``: "pre_norm", "parallel", "gated_post_norm", "sandwich_norm", or one registered there).  ``ffn`` and ``ffn_norm`` may be None: a
     layer that only mixes."""
 
     mixer: PartSpec
@@ -61,6 +61,9 @@ class LayerSpec:
     mixer_gate: PartSpec | None = None
     ffn_gate: PartSpec | None = None
     residual_scale: float = 1.0
+    # For arrangements with a norm on both sides of a sublayer ("sandwich_norm"): the norms of the sublayers' results.
+    mixer_post_norm: PartSpec | None = None
+    ffn_post_norm: PartSpec | None = None
 
     def __post_init__(self) -> None:
         if (self.ffn is None) != (self.ffn_norm is None):

@@ -2,11 +2,14 @@
 //   silu, gelu_tanh (as in the gated kernels), and xielu with two learned numbers (p, q):
 //     z > 0:  softplus(p) z^2 + z/2
 //     z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2
+//   and relu2: max(z, 0)^2.
 #include "common.cuh"
 
 namespace {
 
-enum : int { UNARY_SILU = 0, UNARY_GELU_TANH = 1, UNARY_XIELU = 2 };
+enum : int { UNARY_SILU = 0, UNARY_GELU_TANH = 1, UNARY_XIELU = 2, UNARY_RELU2 = 3 };
+
+__device__ __forceinline__ float relu2f_(float z) { z = fmaxf(z, 0.f); return z * z; }
 
 __device__ __forceinline__ float softplusf_(float x) { return log1pf(expf(-fabsf(x))) + fmaxf(x, 0.f); }
 
@@ -24,6 +27,7 @@ __global__ void unary_act_kernel(const T* __restrict__ x, T* __restrict__ out, s
     const float z = to_float<T>(x[i]);
     float v;
     if (code == UNARY_XIELU) v = z > 0.f ? ap * z * z + 0.5f * z : aq * (expm1f(z) - z) + 0.5f * z;
+    else if (code == UNARY_RELU2) v = relu2f_(z);
     else v = gate_act(z, code);
     out[i] = from_float<T>(v);
   }
@@ -51,6 +55,9 @@ __global__ void unary_act_vec_kernel(const __nv_bfloat16* __restrict__ x, __nv_b
       if (code == UNARY_XIELU) {
         a = z.x > 0.f ? ap * z.x * z.x + 0.5f * z.x : aq * (expm1f(z.x) - z.x) + 0.5f * z.x;
         b = z.y > 0.f ? ap * z.y * z.y + 0.5f * z.y : aq * (expm1f(z.y) - z.y) + 0.5f * z.y;
+      } else if (code == UNARY_RELU2) {
+        a = relu2f_(z.x);
+        b = relu2f_(z.y);
       } else {
         a = gate_act(z.x, code);
         b = gate_act(z.y, code);
@@ -66,7 +73,7 @@ __global__ void unary_act_vec_kernel(const __nv_bfloat16* __restrict__ x, __nv_b
 PSB_API int psb_unary_act(const void* x, int dtype, void* out, long long total, int code, const void* params,
                           cudaStream_t stream) {
   if (total < 0) PSB_REFUSE("unary_act: negative size");
-  if (code < 0 || code > UNARY_XIELU) PSB_REFUSE("unary_act: activation code %d is not built", code);
+  if (code < 0 || code > UNARY_RELU2) PSB_REFUSE("unary_act: activation code %d is not built", code);
   if (code == UNARY_XIELU && !params) PSB_REFUSE("unary_act: xielu needs its two numbers");
   if (total == 0) return 0;
   if (dtype == PSB_BF16 && total % 8 == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0) {

@@ -23,6 +23,23 @@ __global__ void embedding_kernel(const int32_t* __restrict__ ids, const TT* __re
   for (int j = threadIdx.x; j < H; j += blockDim.x) o[j] = to_float<TT>(row[j]);
 }
 
+// h[t] = table[ids[t]] * scale + pos_table[positions[t]]: token rows times a constant plus learned position rows.
+template <typename TT>
+__global__ void embedding_pos_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ positions,
+                                     const TT* __restrict__ table, const TT* __restrict__ pos_table, float* __restrict__ out,
+                                     int H, int V, int P, float scale) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  int id = ids[t], p = positions[t];
+  id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+  p = p < 0 ? 0 : (p >= P ? P - 1 : p);  // positions are checked against the table on the host
+  const TT* row = table + (size_t)id * H;
+  const TT* prow = pos_table + (size_t)p * H;
+  float* o = out + (size_t)t * H;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) o[j] = fmaf(to_float<TT>(row[j]), scale, to_float<TT>(prow[j]));
+}
+
 __device__ __forceinline__ float block_sum(float v, float* scratch) {
   v = warp_sum(v);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
@@ -276,5 +293,18 @@ PSB_API int psb_residual_add(void* h, const void* delta, int delta_dtype, long l
     psb_launch(residual_add_kernel<TD>, dim3(blocks), dim3(256), 0, stream, (float*)h, (const TD*)delta, (size_t)total);
   });
   PSB_LAUNCH_CHECK("residual_add");
+  return 0;
+}
+
+// (ids, positions, table, pos_table, table_dtype, out_f32, T, H, V, P, scale, stream)
+PSB_API int psb_embedding_pos(const void* ids, const void* positions, const void* table, const void* pos_table, int table_dtype,
+                              void* out, int T, int H, int V, int P, float scale, cudaStream_t stream) {
+  if (T < 0 || H < 1 || V < 1 || P < 1) PSB_REFUSE("embedding_pos: bad sizes T=%d H=%d V=%d P=%d", T, H, V, P);
+  if (T == 0) return 0;
+  PSB_DISPATCH_DTYPE(table_dtype, TT, {
+    psb_launch(embedding_pos_kernel<TT>, dim3(T), dim3(H >= 1024 ? 256 : 128), 0, stream, (const int32_t*)ids,
+               (const int32_t*)positions, (const TT*)table, (const TT*)pos_table, (float*)out, H, V, P, scale);
+  });
+  PSB_LAUNCH_CHECK("embedding_pos");
   return 0;
 }

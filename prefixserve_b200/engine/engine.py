@@ -250,17 +250,18 @@ class Engine:
         # page of slack); what is left goes to the groups that keep all keys, which share it page for page.
         by_group = CacheManager.group_page_bytes(self.needs, cfg.page_size, self.dtype)
         sizes: dict[int, int] = {}
-        for gi, (window, cost) in enumerate(by_group.items()):
+        by_group = {(gi, CacheManager.reach_tokens(reach)): cost for gi, (reach, cost) in enumerate(by_group.items())}
+        for (gi, window), cost in by_group.items():
             if window is not None:
                 sizes[gi] = cfg.max_num_seqs * (pages_for(min(cfg.max_seq_len, window + prefill), cfg.page_size) + 1)
                 usable -= sizes[gi] * cost
-        full_cost = sum(cost for window, cost in by_group.items() if window is None)
+        full_cost = sum(cost for (_, window), cost in by_group.items() if window is None)
         need = pages_for(cfg.max_seq_len, cfg.page_size)
         if full_cost:
             n = int(usable // full_cost)
             if n < need:
                 raise EngineError(f"only {n} cache pages fit ({usable / 1e9:.2f} GB usable); one request of max_seq_len needs {need}")
-            for gi, window in enumerate(by_group):
+            for gi, window in by_group:
                 if window is None:
                     sizes[gi] = n
         elif usable < 0:

@@ -400,7 +400,8 @@ class Scheduler:
 
         def most_pages(g) -> int:
             whole = pages_for(total, page)
-            return whole if g.window is None else min(whole, pages_for(g.window + self._chunk, page) + 1)
+            reach = min((x for x in (g.window, g.chunk) if x is not None), default=None)
+            return whole if reach is None else min(whole, pages_for(reach + self._chunk, page) + 1)
 
         checks = (
             (req_id in self._by_id, AddResult.DUPLICATE_ID),

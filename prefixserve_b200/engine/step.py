@@ -202,10 +202,12 @@ class ModelRunner:
         page = cache.page_size
         upto = ((ends + page - 1) // page).astype(np.int32)
         for gi, g in enumerate(cache.groups):
-            if g.window is None:
-                first = np.zeros(len(slots), dtype=np.int32)
-            else:
-                first = (np.maximum(0, starts - g.window + 1) // page).astype(np.int32)
+            low = np.zeros(len(slots), dtype=np.int64)  # the lowest key the step's first token can read
+            if g.window is not None:
+                low = np.maximum(low, starts - g.window + 1)
+            if g.chunk is not None:
+                low = np.maximum(low, starts // g.chunk * g.chunk)
+            first = (low // page).astype(np.int32)
             bad = cache.covered(gi, slots, first, upto)
             if bad >= 0:
                 raise EngineError(f"slot {int(slots[bad])}: page table of group {gi} lacks a page or names one outside the pool")

@@ -31,6 +31,16 @@ class PendingProduct:
         return self._y
 
 
+class PostNormed:
+    """A sublayer's result that joins the stream only after a norm of its own: h += gain * rmsnorm(y).  It travels as the
+    pending output of a block; the norm that meets it next does that sum and its own norm in one kernel
+    (``ops.norm_add_norm``)."""
+
+    def __init__(self, y, gain: torch.Tensor, eps: float):
+        self.y, self.gain, self.eps = y, gain, float(eps)
+        self.shape, self.dtype = tuple(y.shape), y.dtype
+
+
 class NormedRows:
     def __init__(self, h: torch.Tensor, pending, gain: torch.Tensor, eps: float,
                  dtype: torch.dtype, rows: torch.Tensor | None = None):

@@ -10,7 +10,7 @@ import math
 
 import torch
 
-from .deferred import NormedRows, PendingProduct
+from .deferred import NormedRows, PendingProduct, PostNormed
 from .library import KernelError, check, lib, stream_handle
 
 F32, BF16 = 0, 1
@@ -324,6 +324,9 @@ def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
 
 def residual_add(h: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
     """h += delta in place (h float32, delta float32 or bfloat16 of the same shape); returns h."""
+    if isinstance(delta, PostNormed):  # a result that brings its own norm: h += gain * rmsnorm(y)
+        norm_add_norm(h, delta.y, delta.gain, delta.eps)
+        return h
     if isinstance(delta, PendingProduct):
         delta = delta.tensor()
     _dev(h, "residual stream"), _dev(delta, "sublayer output")
@@ -499,7 +502,7 @@ def gated_norm_add(h: torch.Tensor, y: torch.Tensor, gate: torch.Tensor | None, 
     return copy
 
 
-UNARY_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "xielu": 2}  # the codes of activation.cu; xielu takes two learned numbers
+UNARY_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "xielu": 2, "relu2": 3}  # the codes of activation.cu; xielu takes two learned numbers
 
 
 def activation(x: torch.Tensor, name: str, params: torch.Tensor | None = None) -> torch.Tensor:
@@ -703,4 +706,202 @@ def recurrence_scan(proj: torch.Tensor, u: torch.Tensor, gates: torch.Tensor, bi
                                     state.data_ptr(), _i32(ctx.item_start, "item offsets").data_ptr(),
                                     _i32(ctx.slots, "slots").data_ptr(), _ptr(carry), out.data_ptr(), ctx.num_items, t, w, k,
                                     blocks, state.shape[0], chunk, float(decay), _stream()), "recurrence_scan")
+    return out
+
+
+def embedding_positions(ids: torch.Tensor, positions: torch.Tensor, table: torch.Tensor, pos_table: torch.Tensor,
+                        scale: float) -> torch.Tensor:
+    """h[t] = float32(table[ids[t]]) * scale + float32(pos_table[positions[t]])."""
+    _i32(ids, "token ids"), _i32(positions, "positions"), _dev(table, "embedding table"), _dev(pos_table, "position table")
+    t, (v, h) = ids.numel(), table.shape
+    if pos_table.dim() != 2 or pos_table.shape[1] != h or pos_table.dtype != table.dtype or positions.numel() != t:
+        raise KernelError(f"position table {tuple(pos_table.shape)} {pos_table.dtype} does not fit the embedding table {tuple(table.shape)} {table.dtype}")
+    out = torch.empty((t, h), dtype=torch.float32, device=ids.device)
+    check(lib().psb_embedding_pos(ids.data_ptr(), positions.data_ptr(), table.data_ptr(), pos_table.data_ptr(),
+                                  _code(table, "embedding table"), out.data_ptr(), t, h, v, pos_table.shape[0], float(scale),
+                                  _stream()), "embedding_pos")
+    return out
+
+
+def norm_add_norm(h: torch.Tensor, y: torch.Tensor, gain_post: torch.Tensor, eps_post: float,
+                  gain_pre: torch.Tensor | None = None, eps_pre: float = 0.0, out_dtype: torch.dtype | None = None,
+                  rows: torch.Tensor | None = None) -> torch.Tensor | None:
+    """h += gain_post * rmsnorm(y) in place (h float32), and, with ``gain_pre``, returns gain_pre * rmsnorm(new h) in
+    ``out_dtype``: the norm behind one sublayer and the norm in front of the next in one pass.  With ``rows`` only those
+    rows are computed and returned and h is left as it was (the last use of the stream)."""
+    if isinstance(y, PendingProduct):
+        y = y.tensor()
+    _dev(h, "residual stream"), _dev(y, "sublayer output"), _dev(gain_post, "norm gain")
+    if h.dtype != torch.float32 or h.dim() != 2 or y.shape != h.shape:
+        raise KernelError(f"residual stream must be float32 [T, H] and the output must match it: {h.dtype} {tuple(h.shape)} vs {tuple(y.shape)}")
+    n, width = h.shape
+    for g in (gain_post, gain_pre):
+        if g is not None and (g.dtype != torch.float32 or g.numel() != width or not g.is_cuda):
+            raise KernelError(f"norm gain must be float32 [{width}] on the device")
+    if rows is not None:
+        if gain_pre is None:
+            raise KernelError("chosen rows need the second norm")
+        _i32(rows, "row index")
+        n = rows.numel()
+    x = torch.empty((n, width), dtype=out_dtype or torch.float32, device=h.device) if gain_pre is not None else None
+    check(lib().psb_norm_add_norm(h.data_ptr(), y.data_ptr(), _code(y, "sublayer output"), gain_post.data_ptr(), _ptr(gain_pre),
+                                  _ptr(rows), _ptr(x), _code(x, "norm output") if x is not None else F32, n, width,
+                                  float(eps_post), float(eps_pre), _stream()), "norm_add_norm")
+    return x
+
+
+BIASED_TILE_MIN_TOKENS = 16  # portions from this many tokens on go to the kernel that stages keys for a tile of tokens
+
+
+def biased_attention(qkv: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, ctx, *, num_heads: int, num_kv_heads: int,
+                     dim: int, vdim: int, page_size: int, scale: float, window: int | None = None, chunk: int | None = None,
+                     bias: torch.Tensor | None = None, sink: torch.Tensor | None = None) -> torch.Tensor:
+    """The fused projection [T, hq*dim + hkv*dim + hkv*vdim] -> keys and values appended to the pages
+    ([pages, 1, hkv, page_size, dim + vdim]) and causal attention with an optional window, chunk mask, distance bias
+    (float32 [heads, reach]) and sink (float32 [heads]) -> [T, hq * vdim]."""
+    _dev(qkv, "projection output"), _dev(kv, "cache entry"), _i32(table, "page table")
+    positions, token_item = _i32(ctx.positions, "positions"), _i32(ctx.token_item, "token-to-item map")
+    t = qkv.shape[0]
+    want = num_heads * dim + num_kv_heads * (dim + vdim)
+    if qkv.dim() != 2 or qkv.shape[1] != want:
+        raise KernelError(f"projection output must be [T, {want}], is {tuple(qkv.shape)}")
+    if kv.dim() != 5 or tuple(kv.shape[1:]) != (1, num_kv_heads, page_size, dim + vdim):
+        raise KernelError(f"cache entry must be [pages, 1, {num_kv_heads}, {page_size}, {dim + vdim}], is {tuple(kv.shape)}")
+    reach = 0
+    if bias is not None:
+        if bias.dtype != torch.float32 or bias.dim() != 2 or bias.shape[0] != num_heads or not bias.is_cuda or not bias.is_contiguous():
+            raise KernelError(f"distance bias must be float32 [{num_heads}, reach] on the device")
+        reach = bias.shape[1]
+    if sink is not None and (sink.dtype != torch.float32 or sink.numel() != num_heads or not sink.is_cuda):
+        raise KernelError(f"sinks must be float32 [{num_heads}] on the device")
+    q = torch.empty((t, num_heads, dim), dtype=qkv.dtype, device=qkv.device)
+    check(lib().psb_attention_biased_append(qkv.data_ptr(), _code(qkv, "projection output"), positions.data_ptr(),
+                                            token_item.data_ptr(), table.data_ptr(), table.shape[1], kv.data_ptr(),
+                                            _code(kv, "cache entry"), q.data_ptr(), t, num_heads, num_kv_heads, dim, vdim,
+                                            page_size, kv.shape[0], _stream()), "attention_biased_append")
+    out = torch.empty((t, num_heads * vdim), dtype=qkv.dtype, device=qkv.device)
+    win, chk = int(window or 0), int(chunk or 0)
+    # Portions of a bfloat16 step go tile by tile; what is left (single tokens, short portions) walks its keys.  Which
+    # kernel a token gets depends on the length of its portion only (decided on the device from the item offsets, so
+    # the launches have the same shape whatever the step holds); both give the same sums.
+    item_start = _i32(ctx.item_start, "item offsets")
+    tiled = (qkv.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16 and ctx.max_new_tokens >= BIASED_TILE_MIN_TOKENS
+             and bool(lib().psb_attention_biased_tile_supported(num_heads, num_kv_heads, dim, vdim)))
+    if not (tiled and ctx.num_items == 1):  # a step that is one long portion has nothing for the walking kernel
+        check(lib().psb_attention_biased(q.data_ptr(), _code(q, "queries"), kv.data_ptr(), _code(kv, "cache entry"),
+                                         table.data_ptr(), table.shape[1], positions.data_ptr(), token_item.data_ptr(),
+                                         _ptr(bias), _ptr(sink), out.data_ptr(), t, num_heads, num_kv_heads, dim, vdim,
+                                         page_size, win, chk, reach, float(scale), item_start.data_ptr(),
+                                         BIASED_TILE_MIN_TOKENS if tiled else 0, _stream()), "attention_biased")
+    if tiled:
+        check(lib().psb_attention_biased_tiles(q.data_ptr(), kv.data_ptr(), table.data_ptr(), table.shape[1], positions.data_ptr(),
+                                               item_start.data_ptr(), ctx.num_items, t, BIASED_TILE_MIN_TOKENS, _ptr(bias),
+                                               _ptr(sink), out.data_ptr(), num_heads, num_kv_heads, dim, vdim, page_size, win,
+                                               chk, reach, float(scale), _stream()), "attention_biased_tiles")
+    return out
+
+
+DELTA_LONG_PORTION = 32  # steps whose longest portion has this many tokens take 16 lanes a column of the state, else 4
+
+
+def delta_rule(proj: torch.Tensor, ba: torch.Tensor, taps: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
+               gain: torch.Tensor, state: torch.Tensor, ctx, *, groups: int, heads: int, dim: int, vdim: int, eps: float) -> torch.Tensor:
+    """The gated delta rule over every portion of the step.  proj [T, 2*groups*dim + 2*heads*vdim] (queries, keys,
+    values, output gate; compute type), ba float32 [T, 2*heads] (write strength, decay pre-activations), taps float32
+    [2*groups*dim + heads*vdim, K], state float32 [num_slots, (K-1)*channels + heads*dim*vdim].  Returns the normed,
+    gated read-out [T, heads*vdim] in the compute type."""
+    _dev(proj, "projection output"), _dev(ba, "gate pre-activations"), _dev(state, "recurrent state")
+    t = proj.shape[0]
+    c = 2 * groups * dim + heads * vdim
+    k = taps.shape[1]
+    slot_floats = (k - 1) * c + heads * dim * vdim
+    if proj.dim() != 2 or proj.shape[1] != c + heads * vdim or ba.dtype != torch.float32 or tuple(ba.shape) != (t, 2 * heads):
+        raise KernelError(f"delta rule: projection {tuple(proj.shape)} / gates {ba.dtype} {tuple(ba.shape)} do not fit the sizes")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] != slot_floats:
+        raise KernelError(f"delta rule: state must be float32 [slots, {slot_floats}], is {state.dtype} {tuple(state.shape)}")
+    for what, x, n in (("taps", taps, c * k), ("decay rates", a_log, heads), ("decay bias", dt_bias, heads), ("read-out gain", gain, vdim)):
+        if x.dtype != torch.float32 or x.numel() != n or not x.is_cuda or not x.is_contiguous():
+            raise KernelError(f"delta rule: {what} must be float32 with {n} numbers on the device")
+    dev = proj.device
+    qkv = torch.empty((t, c), dtype=torch.float32, device=dev)
+    bd = torch.empty((t, 2 * heads), dtype=torch.float32, device=dev)
+    positions, token_item = _i32(ctx.positions, "positions"), _i32(ctx.token_item, "token-to-item map")
+    item_start, slots = _i32(ctx.item_start, "item offsets"), _i32(ctx.slots, "slots")
+    check(lib().psb_delta_prepare(proj.data_ptr(), _code(proj, "projection output"), ba.data_ptr(), taps.data_ptr(), a_log.data_ptr(),
+                                  dt_bias.data_ptr(), state.data_ptr(), positions.data_ptr(), token_item.data_ptr(),
+                                  item_start.data_ptr(), slots.data_ptr(), qkv.data_ptr(), bd.data_ptr(), t, groups, heads, dim, vdim,
+                                  k, state.shape[0], slot_floats, _stream()), "delta_prepare")
+    o = torch.empty((t, heads, vdim), dtype=torch.float32, device=dev)
+    lanes = 16 if ctx.max_new_tokens >= DELTA_LONG_PORTION and dim >= 32 else 4
+    check(lib().psb_delta_rule(qkv.data_ptr(), bd.data_ptr(), proj.data_ptr(), _code(proj, "projection output"), state.data_ptr(),
+                               item_start.data_ptr(), slots.data_ptr(), o.data_ptr(), ctx.num_items, groups, heads, dim, vdim, k,
+                               state.shape[0], slot_floats, lanes, _stream()), "delta_rule")
+    out = torch.empty((t, heads * vdim), dtype=proj.dtype, device=dev)
+    check(lib().psb_delta_finish(o.data_ptr(), proj.data_ptr(), _code(proj, "projection output"), gain.data_ptr(), out.data_ptr(), t,
+                                 groups, heads, dim, vdim, float(eps), _stream()), "delta_finish")
+    return out
+
+
+def moe_route(z: torch.Tensor, correction: torch.Tensor | None, *, experts: int, top: int, groups: int, keep: int,
+              scale: float):
+    """Router logits float32 [T, >= experts] (further columns are ignored) -> (chosen int32 [T, top], weights float32
+    [T, top]): sigmoid scores, choice by score + correction among the experts of the ``keep`` best of ``groups`` groups,
+    weights = chosen scores / their sum * scale."""
+    _dev(z, "router logits")
+    if z.dtype != torch.float32 or z.dim() != 2 or z.shape[1] < experts:
+        raise KernelError(f"router logits must be float32 [T, >= {experts}], are {z.dtype} {tuple(z.shape)}")
+    if correction is not None and (correction.dtype != torch.float32 or correction.numel() != experts or not correction.is_cuda):
+        raise KernelError(f"router correction must be float32 [{experts}] on the device")
+    t = z.shape[0]
+    chosen = torch.empty((t, top), dtype=torch.int32, device=z.device)
+    weight = torch.empty((t, top), dtype=torch.float32, device=z.device)
+    check(lib().psb_moe_route(z.data_ptr(), z.shape[1], _ptr(correction), chosen.data_ptr(), weight.data_ptr(), t, experts, top,
+                              groups, keep, float(scale), _stream()), "moe_route")
+    return chosen, weight
+
+
+MOE_ACTIVATIONS = {None: 0, "relu2": 1}
+
+
+def moe_experts(x: torch.Tensor, chosen: torch.Tensor, weight: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, *,
+                activation: str = "relu2", shared: torch.Tensor | None = None, shared_gate: torch.Tensor | None = None,
+                out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """sum over a token's chosen experts of weight * down_e(act(up_e x)) (+ sigmoid(shared_gate) * shared), for
+    w_up [E, ff, H], w_down [E, H, ff].  ``shared_gate``: float32 column view [T, 1] (its row stride may be wider)."""
+    _dev(x, "expert input"), _dev(w_up, "expert up matrices"), _dev(w_down, "expert down matrices")
+    _i32(chosen, "chosen experts"), _dev(weight, "expert weights")
+    t, h = x.shape
+    e, ff, _ = w_up.shape
+    top = chosen.shape[1]
+    if tuple(w_up.shape) != (e, ff, h) or tuple(w_down.shape) != (e, h, ff) or tuple(weight.shape) != (t, top) or weight.dtype != torch.float32:
+        raise KernelError(f"experts: up {tuple(w_up.shape)}, down {tuple(w_down.shape)}, weights {tuple(weight.shape)} do not fit {t} tokens of {h}")
+    if activation not in MOE_ACTIVATIONS:
+        raise KernelError(f"experts: activation {activation!r} is not built (one of {sorted(k for k in MOE_ACTIVATIONS if k)})")
+    dev, pairs = x.device, t * top
+    offsets = torch.empty((e + 1,), dtype=torch.int32, device=dev)
+    row_pair = torch.empty((max(pairs, 1),), dtype=torch.int32, device=dev)
+    pair_row = torch.empty((max(pairs, 1),), dtype=torch.int32, device=dev)
+    check(lib().psb_moe_group(chosen.data_ptr(), offsets.data_ptr(), row_pair.data_ptr(), pair_row.data_ptr(), pairs, e, _stream()),
+          "moe_group")
+    mid = torch.empty((pairs, ff), dtype=x.dtype, device=dev)
+    check(lib().psb_moe_gemm(x.data_ptr(), _code(x, "expert input"), w_up.data_ptr(), _code(w_up, "expert up matrices"), mid.data_ptr(),
+                             _code(mid, "expert activations"), offsets.data_ptr(), row_pair.data_ptr(), pairs, e, ff, h, top, 1,
+                             MOE_ACTIVATIONS[activation], _stream()), "moe_gemm")
+    y = torch.empty((pairs, h), dtype=torch.float32, device=dev)
+    check(lib().psb_moe_gemm(mid.data_ptr(), _code(mid, "expert activations"), w_down.data_ptr(), _code(w_down, "expert down matrices"),
+                             y.data_ptr(), F32, offsets.data_ptr(), row_pair.data_ptr(), pairs, e, h, ff, top, 0, 0, _stream()), "moe_gemm")
+    out = torch.empty((t, h), dtype=out_dtype or x.dtype, device=dev)
+    ldg = 0
+    if shared is not None:
+        _dev(shared, "shared expert output")
+        if shared.shape != x.shape:
+            raise KernelError("experts: the shared expert's output must match the input")
+        if shared_gate is not None:
+            if shared_gate.dtype != torch.float32 or shared_gate.shape[0] != t or not shared_gate.is_cuda:
+                raise KernelError("experts: the shared expert's gate must be a float32 column on the device")
+            ldg = shared_gate.stride(0)
+    check(lib().psb_moe_combine(y.data_ptr(), F32, pair_row.data_ptr(), weight.data_ptr(), _ptr(shared),
+                                _code(shared, "shared expert output") if shared is not None else F32,
+                                _ptr(shared_gate) if shared is not None else None, ldg, out.data_ptr(), _code(out, "experts' sum"),
+                                t, h, top, _stream()), "moe_combine")
     return out

@@ -153,6 +153,36 @@ _SIGNATURES: dict[str, list] = {
     #  num_slots, chunk, decay, stream)
     "psb_recurrence_scan": [P, P, I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P],
     "psb_recurrence_max_taps": [],
+    # (ids, positions, table, pos_table, table_dtype, out_f32, T, H, V, P, scale, stream)
+    "psb_embedding_pos": [P, P, P, P, I, P, I, I, I, I, F, P],
+    # (h, y, y_dtype, gain_post, gain_pre, rows, x, x_dtype, n_rows, H, eps_post, eps_pre, stream)
+    "psb_norm_add_norm": [P, P, I, P, P, P, P, I, I, I, F, F, P],
+    # (qkv, dtype, positions, token_item, table, table_width, kv, kv_dtype, q_out, T, hq, hkv, dim, vdim, page_size, num_pages, stream)
+    "psb_attention_biased_append": [P, I, P, P, P, I, P, I, P, I, I, I, I, I, I, I, P],
+    # (q, dtype, kv, kv_dtype, table, table_width, positions, token_item, bias, sink, out, T, hq, hkv, dim, vdim, page_size,
+    #  window, chunk, reach, scale, item_start, skip_from, stream)
+    "psb_attention_biased": [P, I, P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P, I, P],
+    "psb_attention_biased_tile_tokens": [],
+    "psb_attention_biased_tile_supported": [I, I, I, I],
+    # (q, kv, table, table_width, positions, item_start, items, T, min_tokens, bias, sink, out, hq, hkv, dim, vdim,
+    #  page_size, window, chunk, reach, scale, stream)
+    "psb_attention_biased_tiles": [P, P, P, I, P, P, I, I, I, P, P, P, I, I, I, I, I, I, I, I, F, P],
+    "psb_delta_max_taps": [],
+    # (proj, dtype, ba, taps, a_log, dt_bias, state, positions, token_item, item_start, slots, qkv_out, bd_out, T, G, H, dim,
+    #  vdim, K, num_slots, slot_floats, stream)
+    "psb_delta_prepare": [P, I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, L, P],
+    # (qkv, bd, proj, dtype, state, item_start, slots, o_out, items, G, H, dim, vdim, K, num_slots, slot_floats, lanes, stream)
+    "psb_delta_rule": [P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, L, I, P],
+    # (o, proj, dtype, gain, out, T, G, H, dim, vdim, eps, stream)
+    "psb_delta_finish": [P, P, I, P, P, I, I, I, I, I, F, P],
+    # (z, ldz, correction, chosen, weight, T, E, top, groups, keep, scale, stream)
+    "psb_moe_route": [P, I, P, P, P, I, I, I, I, I, F, P],
+    # (chosen, offsets, row_pair, pair_row, pairs, E, stream)
+    "psb_moe_group": [P, P, P, P, I, I, P],
+    # (a, a_dtype, w, w_dtype, c, c_dtype, offsets, row_pair, pairs, E, N, K, top, gather, act, stream)
+    "psb_moe_gemm": [P, I, P, I, P, I, P, P, I, I, I, I, I, I, I, P],
+    # (y, y_dtype, pair_row, weight, shared, shared_dtype, gate, ldg, out, out_dtype, T, H, top, stream)
+    "psb_moe_combine": [P, I, P, P, P, I, P, I, P, I, I, I, I, P],
 }
 
 

@@ -37,6 +37,9 @@ class PagedKV:
     window: int | None = None
     key_order: str = "natural"  # how a key head's elements are ordered in the pages; writer and readers must agree
     planes: int = 2  # 2: keys and values side by side; 1: one row per token that serves as both (a shared latent)
+    # Chunked attention: a query sees only keys of its own run of ``chunk`` positions (runs counted from position 0), so
+    # the pages before the run of the next token are never read again and go back to the pool like pages behind a window.
+    chunk: int | None = None
 
 
 @dataclass(frozen=True)

@@ -8,6 +8,8 @@ The arrangement is chosen by name per layer.  Built in:
 ``gated_post_norm``: the sublayers read the stream itself and the norm sits on their result, behind a gate computed
 from the same input: h += scale * norm_a(mixer(h) * sigmoid(gate_a(h))); then the same with the feed-forward.
 
+``sandwich_norm``: a norm on both sides of each sublayer, h += norm_1b(mixer(norm_1(h))); h += norm_2b(ffn(norm_2(h))).
+
 The residual stream h is float32.  A block takes and returns (h, pending):
 ``pending`` is a sublayer output that has not been added yet, because the sum
 is done inside the next norm's kernel.  An arrangement is a function
@@ -47,13 +49,19 @@ class Block:
         self.mixer_gate = make("gate", spec.mixer_gate) if spec.mixer_gate is not None else None
         self.ffn_gate = make("gate", spec.ffn_gate) if spec.ffn_gate is not None and spec.ffn is not None else None
         self.residual_scale = float(spec.residual_scale)
+        self.mixer_post_norm = make("norm", spec.mixer_post_norm) if spec.mixer_post_norm is not None else None
+        self.ffn_post_norm = make("norm", spec.ffn_post_norm) if spec.ffn_post_norm is not None and spec.ffn is not None else None
 
     def named_parts(self):
         parts = [("mixer_norm", self.mixer_norm), ("mixer", self.mixer)]
+        if self.mixer_post_norm is not None:
+            parts.append(("mixer_post_norm", self.mixer_post_norm))
         if self.mixer_gate is not None:
             parts.append(("mixer_gate", self.mixer_gate))
         if self.ffn is not None:
             parts += [("ffn_norm", self.ffn_norm), ("ffn", self.ffn)]
+            if self.ffn_post_norm is not None:
+                parts.append(("ffn_post_norm", self.ffn_post_norm))
             if self.ffn_gate is not None:
                 parts.append(("ffn_gate", self.ffn_gate))
         return tuple(parts)
@@ -121,6 +129,21 @@ def gated_post_norm(block: Block, h, pending, ctx: StepContext, cache: CacheView
     return h, None
 
 
+def sandwich_norm(block: Block, h, pending, ctx: StepContext, cache: CacheView):
+    """A norm in front of each sublayer and one on its result.  The result travels on as ``pending`` with its norm
+    (``Norm.post``); the next norm in front of a sublayer (this block's, the next block's, or the model's last) adds
+    it to the stream and norms the sum in one kernel."""
+    if block.mixer_post_norm is None or (block.ffn is not None and block.ffn_post_norm is None):
+        raise ValueError("the sandwich_norm arrangement needs a norm for every sublayer's result")
+    y = block.mixer.forward(block.mixer_norm.forward(h, pending, ctx), ctx, cache)
+    pending = block.mixer_post_norm.post(y)
+    if block.ffn is not None:
+        y = block.ffn.forward(block.ffn_norm.forward(h, pending, ctx), ctx)
+        pending = block.ffn_post_norm.post(y)
+    return h, pending
+
+
 register_arrangement("pre_norm", pre_norm)
+register_arrangement("sandwich_norm", sandwich_norm)
 register_arrangement("gated_post_norm", gated_post_norm)
 register_arrangement("parallel", parallel)

@@ -70,6 +70,37 @@ class HashedPairEmbedding(Part):
                                     mul_cur=self.mul_cur, copy_dtype=ctx.compute_dtype)
 
 
+class TokenPositionEmbedding(Part):
+    """Token rows times a constant plus a learned row per absolute position: h = table[token] * scale + positions[p].
+    It reads the step's positions (``uses_step``) but carries nothing from step to step."""
+
+    graph_safe = True  # device work depends only on tensor shapes and device-side inputs
+    uses_step = True   # forward_step(ctx, cache) instead of forward(token_ids)
+
+    def __init__(self, params):
+        super().__init__(params)
+        self.vocab = int(params["vocab_size"])
+        self.hidden = int(params["hidden_size"])
+        self.max_positions = int(params["max_positions"])
+        self.scale = float(params.get("scale", 1.0))
+        self.table: torch.Tensor | None = None
+        self.position_table: torch.Tensor | None = None
+
+    def param_specs(self):
+        return {"weight": ParamSpec((self.vocab, self.hidden)), "position_weight": ParamSpec((self.max_positions, self.hidden))}
+
+    def cache_need(self):
+        from .base import CacheNeed
+        return CacheNeed()
+
+    def load(self, tensors, *, compute_dtype, device):
+        self.table = tensors["weight"].contiguous()
+        self.position_table = tensors["position_weight"].to(self.table.dtype).contiguous()
+
+    def forward_step(self, ctx, cache):
+        return ops.embedding_positions(ctx.token_ids, ctx.positions, self.table, self.position_table, self.scale), None
+
+
 class LMHead(Part):
     graph_safe = True  # device work depends only on tensor shapes and device-side inputs
     takes_deferred_input = True  # x goes to one product only, which may do the norm in front of it itself
@@ -97,4 +128,5 @@ class LMHead(Part):
 
 register_embedding("token_embedding", TokenEmbedding, replace=True)
 register_embedding("hashed_pair_embedding", HashedPairEmbedding, replace=True)
+register_embedding("token_position_embedding", TokenPositionEmbedding, replace=True)
 register_head("lm_head", LMHead, replace=True)

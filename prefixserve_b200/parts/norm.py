@@ -35,7 +35,13 @@ class RMSNorm(Norm):
         self.gain = (1.0 + gain if self.zero_centred else gain).contiguous()
 
     def forward(self, h, delta, ctx: StepContext, rows=None):
+        if isinstance(delta, ops.PostNormed):  # the pending result brings a norm of its own: both norms in one kernel
+            return ops.norm_add_norm(h, delta.y, delta.gain, delta.eps, self.gain, self.eps, ctx.compute_dtype, rows)
         return ops.add_rmsnorm(h, delta, self.gain, self.eps, ctx.compute_dtype, rows)
+
+    def post(self, y) -> "ops.PostNormed":
+        """This norm on a sublayer's result y, to be added to the stream by whoever meets it next."""
+        return ops.PostNormed(y, self.gain, self.eps)
 
     def add_normed(self, h, y, ctx: StepContext, *, gate=None, gate_bias=None, scale: float = 1.0):
         """The norm on a sublayer's result instead of its input: h += scale * norm(y * sigmoid(gate + gate_bias)) in
@@ -45,6 +51,8 @@ class RMSNorm(Norm):
         return h if copy is None else copy
 
     def defer(self, h, delta, ctx: StepContext, rows=None):
+        if isinstance(delta, ops.PostNormed):
+            return ops.NormedRows.ready(self.forward(h, delta, ctx, rows), h)
         return ops.NormedRows(h, delta, self.gain, self.eps, ctx.compute_dtype, rows)
 
 
