@@ -764,13 +764,18 @@ def kernel_costs(base: dict) -> list[tuple[str, float, float]]:
 
 # ------------------------------------------------------------------ another design beside the closest Llama
 NERENEX_SIZES = {"2048": ("nerenex-2048", "1b"), "4096": ("nerenex-4096", "8b")}
+# --workload gekopel: the design's preset and the preset of the closest model already here (Nerenex: layers of a recurrence
+# or an attention over a bounded span of keys, in the same order, at the same width and depth)
+GEKOPEL_SIZES = {"2048": ("gekopel-2048", "nerenex-2048"), "4096": ("gekopel-4096", "nerenex-4096")}
 
 
-def run_nerenex(args) -> dict:
+def run_nerenex(args, design: str = "nerenex") -> dict:
     """--workload nerenex: prefill and decode throughput of the Nerenex design (recurrence, recurrence, latent attention
     with a window; gated post-norm blocks; random weights) at layer sizes of a 1B- and an 8B-class decoder, beside a
     Llama of the same width and number of layers, device-timed, with the time of every kernel name in one prefill step
-    and one decode step (torch profiler; those steps are not the timed ones)."""
+    and one decode step (torch profiler; those steps are not the timed ones).
+    --workload gekopel: the same for the Gekopel design (delta rule, delta rule, chunked attention with a distance bias
+    and a sink; routed experts; sandwich-norm blocks) beside Nerenex at the same width and number of layers."""
     import re
 
     import numpy as np
@@ -783,15 +788,19 @@ def run_nerenex(args) -> dict:
 
     prompt, context, batches = 2048, args.context if "--context" in sys.argv else 2048, (8, 32)
     steps, warmup = min(args.steps, 32), max(3, min(args.warmup, 8))
-    out = {"workload": "nerenex", "dtype": "bf16", "data": "synthetic", "prompt": prompt, "context": context, "steps": steps,
+    sizes = GEKOPEL_SIZES if design == "gekopel" else NERENEX_SIZES
+    out = {"workload": design, "dtype": "bf16", "data": "synthetic", "prompt": prompt, "context": context, "steps": steps,
            "warmup": warmup, "timing": "CUDA events; weights of every model exceed L2", "peaks": peaks(), "sizes": {}}
-    for size in ([args.model] if args.model in NERENEX_SIZES else sorted(NERENEX_SIZES)):
-        own_name, llama_name = NERENEX_SIZES[size]
+    for size in ([args.model] if args.model in sizes else sorted(sizes)):
+        own_name, llama_name = sizes[size]
         n_layers = len(PRESETS[own_name]["layers"])
         entry = out["sizes"][size] = {}
-        for which in ("nerenex", "llama"):
-            if which == "nerenex":
+        for which in ((design, "nerenex") if design == "gekopel" else ("nerenex", "llama")):
+            if which == design:
                 cfg = preset(own_name)
+                vocab = cfg.vocab
+            elif which == "nerenex":
+                cfg = preset(llama_name)
                 vocab = cfg.vocab
             else:
                 from prefixserve_b200.config import LlamaConfig
@@ -937,10 +946,11 @@ def main() -> int:
     p.add_argument("--profile", action="store_true",
                    help="--timeline plus, per kernel, the bytes and flops it has to do in the step and the fraction of the "
                         "measured peak that its time inside the step amounts to")
-    p.add_argument("--workload", choices=["decode", "shared-prefix", "mixed", "nerenex"], default="decode",
+    p.add_argument("--workload", choices=["decode", "shared-prefix", "mixed", "nerenex", "gekopel"], default="decode",
                    help="decode: the headline line.  shared-prefix: 64 requests over 4 system prefixes through the entry "
                         "point, prefix cache on and off.  mixed: steps of one 512-token prompt portion beside 64 decoded tokens.  "
-                        "nerenex: prefill and decode of the Nerenex design beside a Llama of the same width and depth (--model 2048|4096)")
+                        "nerenex: prefill and decode of the Nerenex design beside a Llama of the same width and depth (--model 2048|4096).  "
+                        "gekopel: the same for the Gekopel design beside Nerenex")
     p.add_argument("--model", choices=sorted(SIZES) + sorted(NERENEX_SIZES), default=None,
                    help="layer sizes for --workload shared-prefix (8b) / mixed (3b), and for --only decode (the headline stays 1b)")
     p.add_argument("--requests", type=int, default=64, help="requests of --workload shared-prefix")
@@ -976,8 +986,8 @@ def main() -> int:
             return 0
         if _no_device(args):
             return 1
-        if args.workload == "nerenex":
-            result = run_nerenex(args)
+        if args.workload in ("nerenex", "gekopel"):
+            result = run_nerenex(args, args.workload)
             print(json.dumps(result))
             return 0
         args.model = args.model or ("8b" if args.workload == "shared-prefix" else "3b")

@@ -200,10 +200,11 @@ class CacheManager:
         return reach
 
     def num_pages(self, group: int = 0) -> int:
-        return self.groups[group].pool.num_blocks
+        """Pages of a group's pool (0 for a model that keeps no keys at all: every layer carries a fixed state)."""
+        return self.groups[group].pool.num_blocks if self.groups else 0
 
     def free_pages(self, group: int = 0) -> int:
-        return self.groups[group].pool.num_free
+        return self.groups[group].pool.num_free if self.groups else 0
 
     def cached_pages(self) -> int:
         return self.tree.num_cached_blocks if self.tree is not None else 0

@@ -75,6 +75,36 @@ PRESETS.update({
 })
 
 
+def _gekopel(width: int, vocab: int, groups: int, heads: int, ff: int, chunk: int, experts: int, expert_ff: int) -> dict:
+    """A dense first layer, then ``groups`` times (delta rule, delta rule, chunked attention) with routed experts."""
+    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "shared": {"ff": expert_ff},
+           "router": {"experts": experts, "top": 4, "scale": 2.5, "groups": {"count": 8, "keep": 4}}}
+    attention = {"type": "attention", "mlp": moe,
+                 "mixer": {"heads": heads, "kv_heads": heads // 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                           "bias_max": chunk, "mask": {"size": chunk}}}
+    delta = {"type": "delta", "mlp": moe, "mixer": {"heads": heads, "kv_heads": heads // 2, "dim": 128, "vdim": 128, "conv": 4}}
+    layers = [delta, delta, attention] * groups
+    layers[0] = dict(delta, mlp={"kind": "dense", "ff": ff})
+    return {"architecture": "Gekopel", "vocab": vocab, "width": width, "max_positions": 8192, "norm": {"eps": 1e-6},
+            "embedding": {"scale": 1.0}, "layers": layers}
+
+
+PRESETS.update({
+    "gekopel-tiny": {
+        "architecture": "Gekopel", "vocab": 256, "width": 64, "max_positions": 512, "norm": {"eps": 1e-6}, "embedding": {"scale": 4.0},
+        "layers": [
+            {"type": "delta", "mixer": {"heads": 4, "kv_heads": 2, "dim": 16, "vdim": 24, "conv": 4}, "mlp": {"kind": "dense", "ff": 128}},
+            {"type": "attention", "mixer": {"heads": 4, "kv_heads": 2, "dim": 16, "vdim": 24, "scale": 0.25, "bias_max": 48, "mask": {"size": 40}},
+             "mlp": {"kind": "moe", "expert": {"ff": 32}, "shared": {"ff": 48},
+                     "router": {"experts": 8, "top": 2, "scale": 1.5, "groups": {"count": 4, "keep": 2}}}},
+        ],
+    },
+    # layer sizes of a 1B- and an 8B-class decoder (width, heads), for the benchmarks: per token 4 of 32 experts and a shared one
+    "gekopel-2048": _gekopel(2048, 32768, 4, 16, 8192, 1024, 32, 1024),
+    "gekopel-4096": _gekopel(4096, 32768, 2, 32, 14336, 2048, 32, 2048),
+})
+
+
 def preset(name: str):
     """The typed configuration of a preset, read by its architecture's own reader."""
     try:

@@ -12,15 +12,15 @@
 // from the start of the sequence however the prompt was cut.
 //
 // attention_biased_append_kernel splits a fused projection row [q | k | v] into the query tensor and the cache row.
-// attention_biased_kernel: a warp per (token, query head) walks the visible keys in runs of 32 aligned to absolute
-// positions, a lane per key for the scores, online softmax started from the sink (maximum = sink, sum = 1), the
-// output accumulated in registers.  Scores, weights and sums are float32 and the weights are not rounded before
-// they multiply the values.  Float32 and bfloat16 storage.
+// attention_biased_kernel: a block per (token, query head) walks the visible keys in runs of 32 aligned to absolute
+// positions, its four warps taking the runs in turn, a lane per key for the scores (the key row read 16 bytes at a
+// time), online softmax per warp, the four shares and the sink (maximum = sink, sum = 1, no value) joined at the end.
+// Scores, weights and sums are float32 and the weights are not rounded before they multiply the values.  Float32 and
+// bfloat16 storage.
 //
 // attention_biased_tile_kernel (bfloat16 storage): a block takes 16 consecutive tokens of one request and one
 // key/value head, with all the query heads that share it; key/value rows are staged in shared memory once for the
-// block, a warp takes (token, head) pairs in turn.  Same arithmetic and order of sums as the kernel above, so both
-// give the same numbers for a token.
+// block, a warp takes (token, head) pairs in turn and walks all runs of its pair in order.
 #include <cfloat>
 
 #include "common.cuh"
@@ -54,6 +54,52 @@ __global__ void attention_biased_append_kernel(const T* __restrict__ qkv, const 
   }
 }
 
+// q . k over ``dim`` elements, 16 bytes of the key row at a time where ``vec`` says the row allows it.
+template <typename TKV>
+__device__ __forceinline__ float dot_row(const float* __restrict__ q, const TKV* __restrict__ k, int dim, bool vec);
+template <>
+__device__ __forceinline__ float dot_row<float>(const float* __restrict__ q, const float* __restrict__ k, int dim, bool vec) {
+  float dot = 0.f;
+  if (vec) {
+    for (int d = 0; d < dim; d += 4) {
+      const float4 kv = *reinterpret_cast<const float4*>(k + d);
+      dot = fmaf(q[d], kv.x, dot); dot = fmaf(q[d + 1], kv.y, dot); dot = fmaf(q[d + 2], kv.z, dot); dot = fmaf(q[d + 3], kv.w, dot);
+    }
+  } else {
+    for (int d = 0; d < dim; ++d) dot = fmaf(q[d], k[d], dot);
+  }
+  return dot;
+}
+template <>
+__device__ __forceinline__ float dot_row<__nv_bfloat16>(const float* __restrict__ q, const __nv_bfloat16* __restrict__ k, int dim, bool vec) {
+  float dot = 0.f;
+  if (vec) {
+    // four 16-byte pieces of the row are asked for before the first is used (a lane's row is its own: nothing coalesces)
+    for (int d0 = 0; d0 < dim; d0 += 32) {
+      uint4 raw[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) raw[u] = d0 + 8 * u < dim ? *reinterpret_cast<const uint4*>(k + d0 + 8 * u) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (d0 + 8 * u >= dim) break;
+        const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 kv = __bfloat1622float2(p2[j]);
+          dot = fmaf(q[d0 + 8 * u + 2 * j], kv.x, dot);
+          dot = fmaf(q[d0 + 8 * u + 2 * j + 1], kv.y, dot);
+        }
+      }
+    }
+  } else {
+    for (int d = 0; d < dim; ++d) dot = fmaf(q[d], __bfloat162float(k[d]), dot);
+  }
+  return dot;
+}
+
+// A block per (token, query head); its four warps take the runs of 32 keys in turn (run r of the token, counted from
+// the aligned start of its visible keys, goes to warp r mod 4) and keep a running maximum, sum and output each; warp 0
+// joins the four in warp order.  Which warp gets which run depends on the token's position and the masks only.
 template <typename T, typename TKV>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_biased_kernel(const T* __restrict__ q, const TKV* __restrict__ kv, const int32_t* __restrict__ table,
@@ -61,21 +107,20 @@ attention_biased_kernel(const T* __restrict__ q, const TKV* __restrict__ kv, con
                         const float* __restrict__ bias, const float* __restrict__ sink, T* __restrict__ out, int T_tokens,
                         int hq, int hkv, int dim, int vdim, int page_size, int window, int chunk, int reach, float scale,
                         const int32_t* __restrict__ item_start, int skip_from) {
-  __shared__ float qs[WARPS][MAX_D];
+  __shared__ __align__(16) float qs[MAX_D];
+  __shared__ float part[WARPS][MAX_D + 2];
   pdl_trigger();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long unit = (long long)blockIdx.x * WARPS + warp;
-  if (unit >= (long long)T_tokens * hq) return;
-  const int t = (int)(unit / hq), h = (int)(unit - (long long)t * hq);
+  const int t = blockIdx.x / hq, h = blockIdx.x - t * hq;
   const int g = h / (hq / hkv);
   const int p = positions[t];
   const int item = token_item[t];
   if (skip_from > 0 && item_start[item + 1] - item_start[item] >= skip_from) return;  // the tiled kernel's token
   const int32_t* pages = table + (size_t)item * table_width;
   const T* qrow = q + ((size_t)t * hq + h) * dim;
-  for (int d = lane; d < dim; d += 32) qs[warp][d] = to_float<T>(qrow[d]);
-  __syncwarp();
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) qs[d] = to_float<T>(qrow[d]);
+  __syncthreads();
 
   int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
   if (chunk > 0) lo = max(lo, (p / chunk) * chunk);
@@ -83,14 +128,15 @@ attention_biased_kernel(const T* __restrict__ q, const TKV* __restrict__ kv, con
   const size_t head_stride = (size_t)page_size * rw;
   const size_t page_elems = (size_t)hkv * head_stride;
   const float* brow = bias ? bias + (size_t)h * reach : nullptr;
+  constexpr int PER16 = 16 / (int)sizeof(TKV);
+  const bool vec = dim % PER16 == 0 && rw % PER16 == 0 && (((uintptr_t)kv) & 15) == 0;
 
   float m = -FLT_MAX, l = 0.f;
-  if (sink) { m = sink[h]; l = 1.f; }
   float acc[MAX_D / 32];
 #pragma unroll
   for (int i = 0; i < MAX_D / 32; ++i) acc[i] = 0.f;
 
-  for (int base = lo & ~31; base <= p; base += 32) {
+  for (int base = (lo & ~31) + 32 * warp; base <= p; base += 32 * WARPS) {
     const int key = base + lane;
     const bool live = key >= lo && key <= p;
     long long off = -1;
@@ -98,10 +144,7 @@ attention_biased_kernel(const T* __restrict__ q, const TKV* __restrict__ kv, con
     if (live) {
       const int page = pages[key / page_size];
       off = (long long)((size_t)page * page_elems + (size_t)g * head_stride + (size_t)(key % page_size) * rw);
-      const TKV* krow = kv + off;
-      float dot = 0.f;
-      for (int d = 0; d < dim; ++d) dot = fmaf(qs[warp][d], to_float<TKV>(krow[d]), dot);
-      s = dot * scale;
+      s = dot_row<TKV>(qs, kv + off, dim, vec) * scale;
       if (brow) s += brow[min(p - key, reach - 1)];
     }
     const float m_new = fmaxf(m, warp_max(s));
@@ -112,19 +155,54 @@ attention_biased_kernel(const T* __restrict__ q, const TKV* __restrict__ kv, con
 #pragma unroll
     for (int i = 0; i < MAX_D / 32; ++i) acc[i] *= alpha;
     const int n_live = min(32, p - base + 1);
-    for (int j = 0; j < n_live; ++j) {
-      const float pj = __shfl_sync(0xffffffffu, pr, j);
-      const long long oj = __shfl_sync(0xffffffffu, off, j);
-      if (oj < 0) continue;
-      const TKV* vrow = kv + oj + dim;
+    // eight keys at a time: their value rows are asked for together, then added in key order
+    for (int j0 = 0; j0 < n_live; j0 += 8) {
+      float pj[8];
+      long long oj[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        pj[k] = __shfl_sync(0xffffffffu, pr, (j0 + k) & 31);
+        oj[k] = __shfl_sync(0xffffffffu, off, (j0 + k) & 31);
+      }
 #pragma unroll
       for (int i = 0; i < MAX_D / 32; ++i) {
         const int d = lane + 32 * i;
-        if (d < vdim) acc[i] = fmaf(pj, to_float<TKV>(vrow[d]), acc[i]);
+        if (d < vdim) {
+          float v[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) v[k] = oj[k] >= 0 ? to_float<TKV>(kv[oj[k] + dim + d]) : 0.f;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) acc[i] = fmaf(pj[k], v[k], acc[i]);
+        }
       }
     }
   }
-  const float inv = 1.f / l;
+#pragma unroll
+  for (int i = 0; i < MAX_D / 32; ++i) {
+    const int d = lane + 32 * i;
+    if (d < vdim) part[warp][d] = acc[i];
+  }
+  if (lane == 0) { part[warp][MAX_D] = m; part[warp][MAX_D + 1] = l; }
+  __syncthreads();
+  if (warp != 0) return;
+  // join: the sink first (maximum = sink, sum = 1, no value), then the warps in order
+  float M = sink ? sink[h] : -FLT_MAX, L = sink ? 1.f : 0.f;
+#pragma unroll
+  for (int i = 0; i < MAX_D / 32; ++i) acc[i] = 0.f;
+  for (int w = 0; w < WARPS; ++w) {
+    const float mw = part[w][MAX_D], lw = part[w][MAX_D + 1];
+    if (lw == 0.f) continue;  // a warp without keys
+    const float m_new = fmaxf(M, mw);
+    const float a = expf(M - m_new), b2 = expf(mw - m_new);
+    L = L * a + lw * b2;
+#pragma unroll
+    for (int i = 0; i < MAX_D / 32; ++i) {
+      const int d = lane + 32 * i;
+      if (d < vdim) acc[i] = acc[i] * a + part[w][d] * b2;
+    }
+    M = m_new;
+  }
+  const float inv = 1.f / L;
   T* orow = out + ((size_t)t * hq + h) * vdim;
 #pragma unroll
   for (int i = 0; i < MAX_D / 32; ++i) {
@@ -256,6 +334,201 @@ attention_biased_tile_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
   }
 }
 
+// Prompt portions in bfloat16 on the tensor cores (mma.sync m16n8k16, float32 sums): a block of four warps takes 64
+// consecutive tokens of one request and one query head, a warp 16 of them.  Keys come in blocks of 64 aligned to
+// absolute positions: K as [key][d] and V transposed as [v][key] in shared memory (zeros for keys outside the tile's
+// reach, so nothing of a page that was never written is read).  S = Q K^T stays in the accumulator registers, where
+// scale, bias, masks and the online softmax (started from the sink) are applied in float32; the weights enter the
+// second product as the sum of two bfloat16 numbers (p = hi + lo, two instructions), so they keep 16 bits.
+constexpr int MMA_ROWS = 64, MMA_KEYS = 64;
+
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ void split_bf16(float a, float b, uint32_t& hi, uint32_t& lo) {
+  const __nv_bfloat16 ha = __float2bfloat16_rn(a), hb = __float2bfloat16_rn(b);
+  hi = pack_bf16(a, b);
+  lo = pack_bf16(a - __bfloat162float(ha), b - __bfloat162float(hb));
+}
+
+template <int D, int V>  // key and value sizes rounded up to 64 or 128
+__global__ void __launch_bounds__(128)
+attention_biased_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kv,
+                            const int32_t* __restrict__ table, int table_width, const int32_t* __restrict__ positions,
+                            const int32_t* __restrict__ item_start, int items, int min_tokens, const float* __restrict__ bias,
+                            const float* __restrict__ sink, __nv_bfloat16* __restrict__ out, int hq, int hkv, int dim, int vdim,
+                            int page_size, int window, int chunk, int reach, float scale) {
+  constexpr int KS = D + 8, VS = MMA_KEYS + 8;  // row pitches that keep the fragment loads off each other's banks
+  __shared__ __align__(16) __nv_bfloat16 ks[MMA_KEYS * KS];   // keys [key][d]; first the tile's queries [row][d]
+  __shared__ __align__(16) __nv_bfloat16 vt[V * VS];          // values transposed [v][key]
+  pdl_trigger();
+  pdl_wait();
+  int item = -1, t0 = 0;
+  for (int i = 0, left = blockIdx.x; i < items; ++i) {
+    const int a = item_start[i], n = item_start[i + 1] - a;
+    if (n < min_tokens) continue;
+    const int tiles = (n + MMA_ROWS - 1) / MMA_ROWS;
+    if (left < tiles) { item = i; t0 = a + left * MMA_ROWS; break; }
+    left -= tiles;
+  }
+  if (item < 0) return;
+  const int h = blockIdx.y, g = h / (hq / hkv);
+  const int nt = min(MMA_ROWS, item_start[item + 1] - t0);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
+  const int rw = dim + vdim;
+  const size_t head_stride = (size_t)page_size * rw, page_elems = (size_t)hkv * head_stride;
+  const int32_t* pages = table + (size_t)item * table_width;
+  const int p_first = positions[t0], p_last = p_first + nt - 1;
+
+  // the tile's queries through shared memory into fragments
+  for (int i = threadIdx.x; i < MMA_ROWS * (D / 8); i += blockDim.x) {
+    const int r = i / (D / 8), c = (i - r * (D / 8)) * 8;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < nt && c < dim) v = *reinterpret_cast<const uint4*>(q + ((size_t)(t0 + r) * hq + h) * dim + c);
+    *reinterpret_cast<uint4*>(&ks[r * KS + c]) = v;
+  }
+  __syncthreads();
+  uint32_t qf[D / 16][4];
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+    qf[kk][0] = *reinterpret_cast<const uint32_t*>(&ks[(warp * 16 + gid) * KS + kk * 16 + 2 * tig]);
+    qf[kk][1] = *reinterpret_cast<const uint32_t*>(&ks[(warp * 16 + gid + 8) * KS + kk * 16 + 2 * tig]);
+    qf[kk][2] = *reinterpret_cast<const uint32_t*>(&ks[(warp * 16 + gid) * KS + kk * 16 + 2 * tig + 8]);
+    qf[kk][3] = *reinterpret_cast<const uint32_t*>(&ks[(warp * 16 + gid + 8) * KS + kk * 16 + 2 * tig + 8]);
+  }
+  // this thread's two rows: positions, lowest visible keys, running maximum and its share of the running sum
+  int pos[2], low[2];
+  float m[2], l[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    pos[r] = p_first + warp * 16 + gid + 8 * r;
+    low[r] = (window > 0 && pos[r] - window + 1 > 0) ? pos[r] - window + 1 : 0;
+    if (chunk > 0) low[r] = max(low[r], (pos[r] / chunk) * chunk);
+    m[r] = sink ? sink[h] : -FLT_MAX;
+    l[r] = (sink && tig == 0) ? 1.f : 0.f;
+  }
+  float o[V / 8][4];
+#pragma unroll
+  for (int i = 0; i < V / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  const float* brow = bias ? bias + (size_t)h * reach : nullptr;
+
+  int lo_tile = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
+  if (chunk > 0) lo_tile = max(lo_tile, (p_first / chunk) * chunk);
+  for (int base = lo_tile & ~(MMA_KEYS - 1); base <= p_last; base += MMA_KEYS) {
+    __syncthreads();  // everybody has its query fragments (first round) or is done with the last block
+    for (int i = threadIdx.x; i < MMA_KEYS * (D / 8); i += blockDim.x) {
+      const int j = i / (D / 8), c = (i - j * (D / 8)) * 8;
+      const int key = base + j;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (key >= lo_tile && key <= p_last && c < dim)
+        v = *reinterpret_cast<const uint4*>(kv + (size_t)pages[key / page_size] * page_elems + (size_t)g * head_stride +
+                                            (size_t)(key % page_size) * rw + c);
+      *reinterpret_cast<uint4*>(&ks[j * KS + c]) = v;
+    }
+    for (int i = threadIdx.x; i < MMA_KEYS * (V / 8); i += blockDim.x) {
+      const int j = i % MMA_KEYS, c = (i / MMA_KEYS) * 8;  // neighbouring lanes: neighbouring keys, the same eight value channels
+      const int key = base + j;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (key >= lo_tile && key <= p_last && c < vdim)
+        v = *reinterpret_cast<const uint4*>(kv + (size_t)pages[key / page_size] * page_elems + (size_t)g * head_stride +
+                                            (size_t)(key % page_size) * rw + dim + c);
+      const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) vt[(c + k) * VS + j] = e[k];
+    }
+    __syncthreads();
+    if (base > p_first + warp * 16 + 15) continue;  // all of this warp's rows lie before the block (uniform in the warp)
+    float sc[MMA_KEYS / 8][4];
+#pragma unroll
+    for (int n = 0; n < MMA_KEYS / 8; ++n) {
+      sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&ks[(n * 8 + gid) * KS + kk * 16 + 2 * tig]);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&ks[(n * 8 + gid) * KS + kk * 16 + 2 * tig + 8]);
+        mma_16816(sc[n], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b0, b1);
+      }
+    }
+    float top[2] = {-FLT_MAX, -FLT_MAX};
+#pragma unroll
+    for (int n = 0; n < MMA_KEYS / 8; ++n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int r = e >> 1, key = base + n * 8 + 2 * tig + (e & 1);
+        float v = -INFINITY;
+        if (key <= pos[r] && key >= low[r]) {
+          v = sc[n][e] * scale;
+          if (brow) v += brow[min(pos[r] - key, reach - 1)];
+        }
+        sc[n][e] = v;
+        top[r] = fmaxf(top[r], v);
+      }
+    }
+    float alpha[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      top[r] = fmaxf(top[r], __shfl_xor_sync(0xffffffffu, top[r], 1));
+      top[r] = fmaxf(top[r], __shfl_xor_sync(0xffffffffu, top[r], 2));
+      const float m_new = fmaxf(m[r], top[r]);
+      alpha[r] = expf(m[r] - m_new);
+      m[r] = m_new;
+      l[r] *= alpha[r];
+    }
+#pragma unroll
+    for (int n = 0; n < MMA_KEYS / 8; ++n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float pv = expf(sc[n][e] - m[e >> 1]);  // a masked score is -inf: weight 0
+        sc[n][e] = pv;
+        l[e >> 1] += pv;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < V / 8; ++i) {
+      o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+      o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+    }
+#pragma unroll
+    for (int kk = 0; kk < MMA_KEYS / 16; ++kk) {
+      uint32_t hi[4], lo[4];
+      split_bf16(sc[2 * kk][0], sc[2 * kk][1], hi[0], lo[0]);
+      split_bf16(sc[2 * kk][2], sc[2 * kk][3], hi[1], lo[1]);
+      split_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1], hi[2], lo[2]);
+      split_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3], hi[3], lo[3]);
+#pragma unroll
+      for (int nv = 0; nv < V / 8; ++nv) {
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&vt[(nv * 8 + gid) * VS + kk * 16 + 2 * tig]);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&vt[(nv * 8 + gid) * VS + kk * 16 + 2 * tig + 8]);
+        mma_16816(o[nv], hi[0], hi[1], hi[2], hi[3], b0, b1);
+        mma_16816(o[nv], lo[0], lo[1], lo[2], lo[3], b0, b1);
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = warp * 16 + gid + 8 * r;
+    if (row >= nt) continue;
+    const float inv = 1.f / l[r];
+    __nv_bfloat16* orow = out + ((size_t)(t0 + row) * hq + h) * vdim;
+#pragma unroll
+    for (int nv = 0; nv < V / 8; ++nv) {
+      const int c = nv * 8 + 2 * tig;
+      if (c < vdim) *reinterpret_cast<uint32_t*>(orow + c) = pack_bf16(o[nv][2 * r] * inv, o[nv][2 * r + 1] * inv);
+    }
+  }
+}
+
 size_t tile_smem(int dp, int vp, int share) {
   return sizeof(float) * ((size_t)dp * 33 + 32 * (size_t)vp + (size_t)TILE_T * share * dp + 2 * (size_t)TILE_T * share +
                           (size_t)TILE_T * share * vp);
@@ -299,8 +572,7 @@ PSB_API int psb_attention_biased(const void* q, int dtype, const void* kv, int k
   if (page_size < 1 || table_width < 1) PSB_REFUSE("attention_biased: bad paging (page_size=%d width=%d)", page_size, table_width);
   if (window < 0 || chunk < 0 || (bias && reach < 1)) PSB_REFUSE("attention_biased: negative window or chunk, or an empty bias table");
   if (T == 0) return 0;
-  const long long units = (long long)T * hq;
-  const long long blocks = (units + WARPS - 1) / WARPS;
+  const long long blocks = (long long)T * hq;
   if (blocks > 0x7fffffffLL) PSB_REFUSE("attention_biased: batch too large");
   PSB_DISPATCH_DTYPE(dtype, T_, {
     PSB_DISPATCH_DTYPE(kv_dtype, TKV, {
@@ -311,6 +583,38 @@ PSB_API int psb_attention_biased(const void* q, int dtype, const void* kv, int k
     });
   });
   PSB_LAUNCH_CHECK("attention_biased");
+  return 0;
+}
+
+// (hq, hkv, dim, vdim) -> 1 if the tensor-core kernel for prompt portions takes the shape
+PSB_API int psb_attention_biased_mma_supported(int hq, int hkv, int dim, int vdim) {
+  return hq >= 1 && hkv >= 1 && hq % hkv == 0 && dim >= 8 && dim <= 128 && dim % 8 == 0 && vdim >= 8 && vdim <= 128 && vdim % 8 == 0 ? 1 : 0;
+}
+
+// The tensor-core kernel over every portion of at least ``min_tokens`` tokens (bfloat16; grid sized by an upper bound on
+// the 64-token tiles).  Other tokens are left untouched.
+// (q, kv, table, table_width, positions, item_start, items, T, min_tokens, bias, sink, out, hq, hkv, dim, vdim,
+//  page_size, window, chunk, reach, scale, stream)
+PSB_API int psb_attention_biased_mma(const void* q, const void* kv, const void* table, int table_width, const void* positions,
+                                     const void* item_start, int items, int T, int min_tokens, const void* bias, const void* sink,
+                                     void* out, int hq, int hkv, int dim, int vdim, int page_size, int window, int chunk, int reach,
+                                     float scale, cudaStream_t stream) {
+  if (!psb_attention_biased_mma_supported(hq, hkv, dim, vdim)) PSB_REFUSE("attention_biased_mma: shape not taken");
+  if (page_size < 1 || table_width < 1 || window < 0 || chunk < 0 || (bias && reach < 1)) PSB_REFUSE("attention_biased_mma: bad arguments");
+  if ((((uintptr_t)q | (uintptr_t)kv) & 15) || hq > 65535) PSB_REFUSE("attention_biased_mma: operands must be 16-byte aligned");
+  if (items < 1 || T < 1 || min_tokens < 1) return 0;
+  const dim3 grid((T + MMA_ROWS - 1) / MMA_ROWS + items, hq), block(128);
+#define MMA_CASE(D_, V_)                                                                                                       \
+  psb_launch(attention_biased_mma_kernel<D_, V_>, grid, block, 0, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)kv,    \
+             (const int32_t*)table, table_width, (const int32_t*)positions, (const int32_t*)item_start, items, min_tokens,     \
+             (const float*)bias, (const float*)sink, (__nv_bfloat16*)out, hq, hkv, dim, vdim, page_size, window, chunk, reach, \
+             scale)
+  if (dim <= 64 && vdim <= 64) MMA_CASE(64, 64);
+  else if (dim <= 64) MMA_CASE(64, 128);
+  else if (vdim <= 64) MMA_CASE(128, 64);
+  else MMA_CASE(128, 128);
+#undef MMA_CASE
+  PSB_LAUNCH_CHECK("attention_biased_mma");
   return 0;
 }
 

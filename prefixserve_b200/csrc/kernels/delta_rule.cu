@@ -5,7 +5,7 @@
 // values of H heads, then the output gate (H vdim).  A second small product gives, in float32, the pre-activations
 // of the write strength and of the decay, [T, 2 H].
 //
-// delta_prepare_kernel (a block per token): every query, key and value channel goes through a short causal
+// delta_prepare_kernel (a block per token and query group, key group or value head): every query, key and value channel goes through a short causal
 // convolution over its last K inputs (weights [channels, K], the last column the current token's, no bias, zeros
 // before the start of the sequence; inputs from before the portion are read from the request's slot) and SiLU.
 // Queries and keys are made unit vectors per group, x / sqrt(sum x^2 + 1e-6), queries also times dim^-1/2.  Per
@@ -17,8 +17,8 @@
 // so the read-out sees the current token's write.  The columns of S (one per value channel) never meet: R lanes of
 // a warp hold one column between them (dim / R numbers each, in registers), so a warp carries 32 / R columns, and
 // the two dot products of a token are finished by a butterfly among the R lanes.  The order of every sum depends on
-// R and dim only, never on the batch.  Queries and keys of a run of tokens are staged in shared memory for the whole
-// block.  The state is read from the request's slot at the portion's start and written back at its end; one block
+// R and dim only, never on the batch.  What a run of tokens brings is staged in shared memory for the whole block, one
+// run ahead of the arithmetic.  The state is read from the request's slot at the portion's start and written back at its end; one block
 // per request also brings the slot's convolution inputs up to date (the last K-1 rows of the projection, or what
 // was there before, moved up, when the portion is shorter).
 //
@@ -36,75 +36,101 @@ __device__ __forceinline__ float softplusf_(float x) { return log1pf(expf(-fabsf
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-x)); }
 __device__ __forceinline__ float siluf_(float x) { return x / (1.f + expf(-x)); }
 
+// A block per (token, unit); a unit is one query group, one key group (dim channels each) or one value head (vdim).
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 delta_prepare_kernel(const T* __restrict__ proj, const float* __restrict__ ba, const float* __restrict__ taps,
                      const float* __restrict__ a_log, const float* __restrict__ dt_bias, const float* __restrict__ state,
                      const int32_t* __restrict__ positions, const int32_t* __restrict__ token_item,
                      const int32_t* __restrict__ item_start, const int32_t* __restrict__ slots, float* __restrict__ qkv,
-                     float* __restrict__ bd, int G, int H, int dim, int vdim, int K, int num_slots, size_t slot_floats) {
-  extern __shared__ float row[];  // [C] the token's convolved, activated channels
-  __shared__ float factor[64];
+                     float* __restrict__ bd, int G, int H, int dim, int vdim, int K, int num_slots, size_t slot_floats,
+                     int T_tokens, int tokens_per_block) {
+  extern __shared__ float row[];  // the unit's convolved, activated channels
+  __shared__ float scratch[4];
   pdl_trigger();
-  const int t = blockIdx.x;
+  const int unit = blockIdx.y;
   const int C = 2 * G * dim + H * vdim, P = C + H * vdim;
+  const int c0 = unit < 2 * G ? unit * dim : 2 * G * dim + (unit - 2 * G) * vdim;
+  const int len = unit < 2 * G ? dim : vdim;
   pdl_wait();
+  for (int t = blockIdx.x * tokens_per_block; t < min(T_tokens, (blockIdx.x + 1) * tokens_per_block); ++t) {
+  __syncthreads();  // the last token's row and sums have been read
   const int item = token_item[t];
   const int p = positions[t], p0 = positions[item_start[item]];
   int slot = slots[item];
   slot = slot < 0 ? 0 : (slot >= num_slots ? num_slots - 1 : slot);
   const float* tail = state + (size_t)slot * slot_floats;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < len; i += blockDim.x) {
+    const int c = c0 + i;
+    float x[MAX_TAPS];
+#pragma unroll
+    for (int k = 0; k < MAX_TAPS; ++k) {  // the inputs under the taps, asked for together
+      if (k >= K) break;
+      const int src = p - (K - 1) + k;
+      x[k] = 0.f;
+      if (src >= p0) x[k] = to_float<T>(proj[(size_t)(t - (p - src)) * P + c]);
+      else if (src >= 0) x[k] = tail[(size_t)(src - p0 + K - 1) * C + c];
+    }
     float acc = 0.f;
-    for (int k = 0; k < K; ++k) {
-      const int src = p - (K - 1) + k;  // position of the input under tap k
-      float x = 0.f;
-      if (src >= p0) x = to_float<T>(proj[(size_t)(t - (p - src)) * P + c]);
-      else if (src >= 0) x = tail[(size_t)(src - p0 + K - 1) * C + c];
-      acc = fmaf(taps[(size_t)c * K + k], x, acc);
+#pragma unroll
+    for (int k = 0; k < MAX_TAPS; ++k) {
+      if (k >= K) break;
+      acc = fmaf(taps[(size_t)c * K + k], x[k], acc);
     }
-    row[c] = siluf_(acc);
+    const float v = siluf_(acc);
+    row[i] = v;
+    ss = fmaf(v, v, ss);
   }
-  __syncthreads();
-  // unit vectors: 2 G groups of dim channels (queries first), a warp per group in turn
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-  for (int g0 = 0; g0 < 2 * G; g0 += 64) {
-    for (int g = g0 + warp; g < min(2 * G, g0 + 64); g += warps) {
-      float ss = 0.f;
-      for (int d = lane; d < dim; d += 32) ss = fmaf(row[g * dim + d], row[g * dim + d], ss);
-      ss = warp_sum(ss);
-      if (lane == 0) factor[g - g0] = (g < G ? rsqrtf((float)dim) : 1.f) / sqrtf(ss + 1e-6f);
+  float factor = 1.f;
+  if (unit < 2 * G) {  // unit vectors; queries also times dim^-1/2
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    const float total = scratch[0] + scratch[1] + scratch[2] + scratch[3];
+    factor = (unit < G ? rsqrtf((float)dim) : 1.f) / sqrtf(total + 1e-6f);
+  }
+  float* out = qkv + (size_t)t * C + c0;
+  for (int i = threadIdx.x; i < len; i += blockDim.x) out[i] = row[i] * factor;  // a thread reads back what it wrote
+  if (unit == 0) {
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+      bd[(size_t)t * 2 * H + h] = sigmoidf_(ba[(size_t)t * 2 * H + h]);
+      bd[(size_t)t * 2 * H + H + h] = expf(-expf(a_log[h]) * softplusf_(ba[(size_t)t * 2 * H + H + h] + dt_bias[h]));
     }
-    __syncthreads();
-    for (int c = g0 * dim + threadIdx.x; c < min(2 * G, g0 + 64) * dim; c += blockDim.x) row[c] *= factor[c / dim - g0];
-    __syncthreads();
   }
-  float* out = qkv + (size_t)t * C;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) out[c] = row[c];
-  for (int h = threadIdx.x; h < H; h += blockDim.x) {
-    bd[(size_t)t * 2 * H + h] = sigmoidf_(ba[(size_t)t * 2 * H + h]);
-    bd[(size_t)t * 2 * H + H + h] = expf(-expf(a_log[h]) * softplusf_(ba[(size_t)t * 2 * H + H + h] + dt_bias[h]));
   }
 }
 
 constexpr int RULE_WARPS = 4;
-constexpr int STAGE_TOKENS = 8;  // tokens whose queries and keys are staged together
 
-// PER: numbers of a column one lane holds; R: lanes per column.  R * PER >= dim.
+__device__ __forceinline__ void copy_async4(float* dst, const float* src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copy_async_wait() {
+  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+}
+
+// PER: numbers of a column one lane holds; R: lanes per column.  R * PER >= dim.  What the tokens of a stage bring
+// (queries, keys, the block's value columns, beta, decay) is copied into shared memory one stage ahead of the
+// arithmetic (cp.async into the other of two buffers), so the chain from token to token never waits for memory.
 template <typename T, int PER, int R>
 __global__ void __launch_bounds__(RULE_WARPS * 32)
 delta_rule_kernel(const float* __restrict__ qkv, const float* __restrict__ bd, const T* __restrict__ proj,
                   float* __restrict__ state, const int32_t* __restrict__ item_start, const int32_t* __restrict__ slots,
-                  float* __restrict__ o, int G, int H, int dim, int vdim, int K, int num_slots, size_t slot_floats) {
-  __shared__ float qk[STAGE_TOKENS][2][R * PER];
+                  float* __restrict__ o, int G, int H, int dim, int vdim, int K, int num_slots, size_t slot_floats,
+                  int stage_tokens) {
+  extern __shared__ float staged[];  // [2][stage_tokens][W]
   constexpr int COLS = 32 / R;  // columns a warp holds
+  constexpr int RP = R * PER, BC = RULE_WARPS * COLS, W = 2 * RP + BC + 2;
   pdl_trigger();
   const int C = 2 * G * dim + H * vdim, P = C + H * vdim;
   const int h = blockIdx.y, item = blockIdx.z;
   const int g = h / (H / G);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = lane % R;
-  const int col = (blockIdx.x * RULE_WARPS + warp) * COLS + lane / R;
+  const int col0 = blockIdx.x * BC, in_block = warp * COLS + lane / R;
+  const int col = col0 + in_block;
   const bool live = col < vdim;
   pdl_wait();
   const int t0 = item_start[item], t1 = item_start[item + 1];
@@ -112,45 +138,74 @@ delta_rule_kernel(const float* __restrict__ qkv, const float* __restrict__ bd, c
   slot = slot < 0 ? 0 : (slot >= num_slots ? num_slots - 1 : slot);
   float* base = state + (size_t)slot * slot_floats;
   float* S = base + (size_t)(K - 1) * C + (size_t)h * dim * vdim;
+
+  auto stage = [&](int ts, float* buf) {  // tokens ts .. ts + stage_tokens - 1 (those before t1) into buf
+    const int n = min(stage_tokens, t1 - ts);
+    for (int i = threadIdx.x; i < n * W; i += blockDim.x) {
+      const int tok = i / W, e = i - tok * W;
+      const float* row = qkv + (size_t)(ts + tok) * C;
+      const float* src = nullptr;
+      if (e < 2 * RP) {
+        const int which = e / RP, d = e - which * RP;
+        if (d < dim) src = row + (size_t)which * G * dim + g * dim + d;
+      } else if (e < 2 * RP + BC) {
+        if (col0 + e - 2 * RP < vdim) src = row + 2 * G * dim + h * vdim + col0 + e - 2 * RP;
+      } else {
+        src = bd + (size_t)(ts + tok) * 2 * H + (e - 2 * RP - BC) * H + h;
+      }
+      if (src) copy_async4(buf + i, src);
+      else buf[i] = 0.f;
+    }
+  };
+
+  if (t1 > t0) stage(t0, staged);
   float s[PER];
 #pragma unroll
   for (int e = 0; e < PER; ++e) {
     const int d = r * PER + e;
     s[e] = (live && d < dim) ? S[(size_t)d * vdim + col] : 0.f;
   }
-  for (int ts = t0; ts < t1; ts += STAGE_TOKENS) {
-    const int n = min(STAGE_TOKENS, t1 - ts);
-    __syncthreads();
-    for (int i = threadIdx.x; i < n * 2 * R * PER; i += blockDim.x) {
-      const int tok = i / (2 * R * PER), rest = i - tok * 2 * R * PER;
-      const int which = rest / (R * PER), d = rest - which * R * PER;
-      qk[tok][which][d] = d < dim ? qkv[(size_t)(ts + tok) * C + (size_t)which * G * dim + g * dim + d] : 0.f;
-    }
-    __syncthreads();
+  int which_buf = 0;
+  for (int ts = t0; ts < t1; ts += stage_tokens, which_buf ^= 1) {
+    const int n = min(stage_tokens, t1 - ts);
+    copy_async_wait();
+    __syncthreads();  // this stage has landed for everybody, and everybody has left the other buffer
+    if (ts + stage_tokens < t1) stage(ts + stage_tokens, staged + (size_t)(which_buf ^ 1) * stage_tokens * W);
+    const float* buf = staged + (size_t)which_buf * stage_tokens * W;
     for (int i = 0; i < n; ++i) {
-      const int t = ts + i;
-      const float beta = bd[(size_t)t * 2 * H + h], dec = bd[(size_t)t * 2 * H + H + h];
-      const float v = live ? qkv[(size_t)t * C + 2 * G * dim + h * vdim + col] : 0.f;
-      const float* kk = &qk[i][1][r * PER];
-      const float* qq = &qk[i][0][r * PER];
-      float kd = 0.f;
+      const float* tokrow = buf + i * W;
+      const float* qq = tokrow + r * PER;
+      const float* kk = tokrow + RP + r * PER;
+      const float v = tokrow[2 * RP + in_block];
+      const float beta = tokrow[2 * RP + BC], dec = tokrow[2 * RP + BC + 1];
+      float kd0 = 0.f, kd1 = 0.f;
 #pragma unroll
-      for (int e = 0; e < PER; ++e) {
+      for (int e = 0; e < PER; e += 2) {
         s[e] *= dec;
-        kd = fmaf(kk[e], s[e], kd);
+        kd0 = fmaf(kk[e], s[e], kd0);
+        if (e + 1 < PER) {
+          s[e + 1] *= dec;
+          kd1 = fmaf(kk[e + 1], s[e + 1], kd1);
+        }
       }
+      float kd = kd0 + kd1;
 #pragma unroll
       for (int off = 1; off < R; off <<= 1) kd += __shfl_xor_sync(0xffffffffu, kd, off);
       const float u = beta * (v - kd);
-      float od = 0.f;
+      float od0 = 0.f, od1 = 0.f;
 #pragma unroll
-      for (int e = 0; e < PER; ++e) {
+      for (int e = 0; e < PER; e += 2) {
         s[e] = fmaf(kk[e], u, s[e]);
-        od = fmaf(qq[e], s[e], od);
+        od0 = fmaf(qq[e], s[e], od0);
+        if (e + 1 < PER) {
+          s[e + 1] = fmaf(kk[e + 1], u, s[e + 1]);
+          od1 = fmaf(qq[e + 1], s[e + 1], od1);
+        }
       }
+      float od = od0 + od1;
 #pragma unroll
       for (int off = 1; off < R; off <<= 1) od += __shfl_xor_sync(0xffffffffu, od, off);
-      if (live && r == 0) o[((size_t)t * H + h) * vdim + col] = od;
+      if (live && r == 0) o[((size_t)(ts + i) * H + h) * vdim + col] = od;
     }
   }
 #pragma unroll
@@ -204,8 +259,12 @@ template <typename T, int PER, int R>
 void launch_rule(dim3 grid, cudaStream_t stream, const float* qkv, const float* bd, const T* proj, float* state,
                  const int32_t* item_start, const int32_t* slots, float* o, int G, int H, int dim, int vdim, int K,
                  int num_slots, size_t slot_floats) {
-  psb_launch(delta_rule_kernel<T, PER, R>, grid, dim3(RULE_WARPS * 32), 0, stream, qkv, bd, proj, state, item_start, slots, o,
-             G, H, dim, vdim, K, num_slots, slot_floats);
+  constexpr int W = 2 * R * PER + RULE_WARPS * (32 / R) + 2;
+  // two buffers within the 48 KB a kernel has without asking: 16 tokens a stage for keys up to 128 numbers, 4 beyond
+  const int stage_tokens = 2 * 16 * W * (int)sizeof(float) <= 48 * 1024 ? 16 : 4;
+  static_assert(2 * 4 * W * sizeof(float) <= 48 * 1024, "a stage of four tokens fits the default shared memory twice");
+  psb_launch(delta_rule_kernel<T, PER, R>, grid, dim3(RULE_WARPS * 32), (size_t)2 * stage_tokens * W * sizeof(float), stream, qkv,
+             bd, proj, state, item_start, slots, o, G, H, dim, vdim, K, num_slots, slot_floats, stage_tokens);
 }
 
 }  // namespace
@@ -222,14 +281,15 @@ PSB_API int psb_delta_prepare(const void* proj, int dtype, const void* ba, const
   if (K < 1 || K > MAX_TAPS) PSB_REFUSE("delta_prepare: %d taps are outside [1, %d]", K, MAX_TAPS);
   const long long C = 2LL * G * dim + (long long)H * vdim;
   if (slot_floats != (K - 1) * C + (long long)H * dim * vdim) PSB_REFUSE("delta_prepare: a slot of %lld numbers does not fit the sizes", slot_floats);
-  const size_t smem = (size_t)C * sizeof(float);
-  if (smem > 48 * 1024) PSB_REFUSE("delta_prepare: %lld channels exceed the kernel's shared memory", C);
+  const size_t smem = (size_t)(dim > vdim ? dim : vdim) * sizeof(float);
+  if (smem > 48 * 1024 || 2 * G + H > 65535) PSB_REFUSE("delta_prepare: sizes exceed the kernel's shared memory or grid");
   if (T == 0) return 0;
   PSB_DISPATCH_DTYPE(dtype, T_, {
-    psb_launch(delta_prepare_kernel<T_>, dim3(T), dim3(256), smem, stream, (const T_*)proj, (const float*)ba, (const float*)taps,
-               (const float*)a_log, (const float*)dt_bias, (const float*)state, (const int32_t*)positions,
-               (const int32_t*)token_item, (const int32_t*)item_start, (const int32_t*)slots, (float*)qkv, (float*)bd, G, H, dim,
-               vdim, K, num_slots, (size_t)slot_floats);
+    const int per_block = T >= 1024 ? 8 : 1;  // long steps: a block stays with its unit for eight tokens
+    psb_launch(delta_prepare_kernel<T_>, dim3((T + per_block - 1) / per_block, 2 * G + H), dim3(128), smem, stream, (const T_*)proj,
+               (const float*)ba, (const float*)taps, (const float*)a_log, (const float*)dt_bias, (const float*)state,
+               (const int32_t*)positions, (const int32_t*)token_item, (const int32_t*)item_start, (const int32_t*)slots,
+               (float*)qkv, (float*)bd, G, H, dim, vdim, K, num_slots, (size_t)slot_floats, T, per_block);
   });
   PSB_LAUNCH_CHECK("delta_prepare");
   return 0;

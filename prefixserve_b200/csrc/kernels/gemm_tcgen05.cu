@@ -68,7 +68,13 @@ using namespace tc;
 // mode: 0 plain (C[M, N], tile columns [n0, n0+BN/2) and [n0+BN/2, n0+BN)); 1 gated (C[M, I], W = [gate; up], tile
 // columns [n0, n0+128) of the gate and the same of the up rows); 2 the projection of an attention layer (columns as in
 // 0; the epilogue rotates queries and keys and stores queries, keys and values where RopeArgs says, C is not used).
-enum : int { MODE_PLAIN = 0, MODE_GATED = 1, MODE_ROPE = 2, MODE_GATED_GELU = 3 };  // gated: SiLU, or the tanh form of GELU
+enum : int { MODE_PLAIN = 0, MODE_GATED = 1, MODE_ROPE = 2, MODE_GATED_GELU = 3, MODE_RELU2 = 4 };  // gated: SiLU, or the tanh form of GELU
+// MODE_RELU2: columns as in 0, the epilogue stores max(sum, 0)^2.
+//
+// Grouped products (``tile_expert`` given): W is a stack of matrices [experts * N_out, K] and every 128-row tile of A
+// belongs to one of them, named by tile_expert[row tile] (-1: the tile holds no rows and is skipped by all three
+// roles alike); the W rows of the tile start at expert * N_out.  Columns of a tile beyond N_out read the next matrix's
+// rows and are never stored.
 
 // One thread's row of a 128 x BN tile of sums, for the projection of an attention layer: 16 columns are 8 pairs of one
 // head (first-half elements, then the ones they are rotated with), so the job of the rotary kernel is done on the sums
@@ -151,7 +157,7 @@ template <int BN, int HB>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     __nv_bfloat16* __restrict__ C, int M, int N_out, int K, int ldc, int up_offset, int mode,
-                    const RopeArgs rope) {
+                    const RopeArgs rope, const int32_t* __restrict__ tile_expert) {
   using T = Tile<BN>;
   constexpr int BN_HALF = T::HALF, STAGES = T::STAGES, STAGE_BYTES = T::STAGE_BYTES;
   constexpr uint32_t INSTR_DESC = instr_desc(BM, BN, false);  // M=128, N=BN, both operands K-major
@@ -197,7 +203,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < tiles_total; tile += gridDim.x) {
         const int m0 = (tile % m_blocks) * BM;
-        const int n0 = (tile / m_blocks) * n_span;
+        int n0 = (tile / m_blocks) * n_span;
+        if (tile_expert) {
+          const int expert = tile_expert[tile % m_blocks];
+          if (expert < 0) continue;
+          n0 += expert * N_out;
+        }
         const int n1 = gated ? up_offset + n0 : n0 + BN_HALF;
         for (int kb = 0; kb < k_blocks; ++kb) {
           ok = mbar_wait(&bars->empty[stage], phase ^ 1, abort, 1);
@@ -219,8 +230,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     {
       uint32_t stage = 0, phase = 0, local = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < tiles_total; tile += gridDim.x, ++local) {
+      for (int tile = blockIdx.x; ok && tile < tiles_total; tile += gridDim.x) {
+        if (tile_expert && tile_expert[tile % m_blocks] < 0) continue;  // an empty tile uses no accumulator buffer
         const uint32_t buf = local & 1, use = local >> 1;  // accumulator buffer and how often it has been used
+        ++local;
         ok = mbar_wait(&bars->acc_empty[buf], (use & 1) ^ 1, abort, 4);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -248,8 +261,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int quarter = warp & 3;  // a warp may only read tensor-memory lanes [32*(warp%4), +32)
     uint32_t local = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < tiles_total; tile += gridDim.x, ++local) {
+    for (int tile = blockIdx.x; ok && tile < tiles_total; tile += gridDim.x) {
+      if (tile_expert && tile_expert[tile % m_blocks] < 0) continue;
       const uint32_t buf = local & 1, use = local >> 1;
+      ++local;
       const int m0 = (tile % m_blocks) * BM;
       const int n0 = (tile / m_blocks) * n_span;
       const int row = m0 + quarter * 32 + lane;
@@ -322,7 +337,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
               const int col = n0 + c + j;
               uint32_t packed[4];
 #pragma unroll
-              for (int q = 0; q < 4; ++q) packed[q] = pack2(__uint_as_float(v[j + 2 * q]), __uint_as_float(v[j + 2 * q + 1]));
+              for (int q = 0; q < 4; ++q) {
+                float v0 = __uint_as_float(v[j + 2 * q]), v1 = __uint_as_float(v[j + 2 * q + 1]);
+                if (mode == MODE_RELU2) {
+                  v0 = fmaxf(v0, 0.f), v1 = fmaxf(v1, 0.f);
+                  v0 *= v0, v1 *= v1;
+                }
+                packed[q] = pack2(v0, v1);
+              }
               if (col + 8 <= N_out && (ldc & 7) == 0) {
                 *reinterpret_cast<uint4*>(crow + col) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
               } else {
@@ -387,7 +409,7 @@ int choose_width(int M, int N_out, bool gated, bool rope, int D, int sms) {
 }
 
 int launch(const void* a, const void* w, void* c, int M, int w_rows, int N_out, int K, int up_offset, int mode, int sms,
-           cudaStream_t stream, const RopeArgs& rope = RopeArgs{}) {
+           cudaStream_t stream, const RopeArgs& rope = RopeArgs{}, const int32_t* tile_expert = nullptr) {
   const bool gated = mode == MODE_GATED || mode == MODE_GATED_GELU;
   if (M < 1 || N_out < 1 || K < 8 || K % 8) PSB_REFUSE("gemm_tcgen05: needs K a multiple of 8 (M=%d N=%d K=%d)", M, N_out, K);
   if (((uintptr_t)a | (uintptr_t)w | (uintptr_t)c) & 15) PSB_REFUSE("gemm_tcgen05: operands must be 16-byte aligned");
@@ -409,7 +431,7 @@ int launch(const void* a, const void* w, void* c, int M, int w_rows, int N_out, 
       configured.set();                                                                                              \
     }                                                                                                                \
     psb_launch(gemm_tcgen05_kernel<BN, HB>, dim3(grid), dim3(THREADS), (size_t)Tile<BN>::SMEM_BYTES, stream, map_a,   \
-               map_w, (__nv_bfloat16*)c, M, N_out, K, N_out, up_offset, mode, rope);                                 \
+               map_w, (__nv_bfloat16*)c, M, N_out, K, N_out, up_offset, mode, rope, tile_expert);                    \
   } while (0)
   // the usual head sizes keep a row's angles in registers; every other multiple of 16 fetches them block by block
   if (mode == MODE_ROPE && rope.D == 128) { if (bn == 128) PSB_TCGEN05(128, 8); else PSB_TCGEN05(256, 8); }
@@ -435,6 +457,16 @@ PSB_API int psb_gemm_tcgen05_gated(const void* a, const void* w, void* act, int 
                                    cudaStream_t stream) {
   if (!psb_activation_known(activation)) PSB_REFUSE("gemm_tcgen05_gated: activation code %d is not built", activation);
   return launch(a, w, act, M, 2 * I, I, K, I, activation == PSB_ACT_SILU ? MODE_GATED : MODE_GATED_GELU, sms, stream);
+}
+
+// Grouped: C[M, N] = act(A[M, K] W[e]^T) where W is [experts, N, K] and the rows of A lie expert by expert, every
+// expert's rows starting at a multiple of 128; tile_expert [M / 128 rounded up] (device) names the expert of every
+// 128-row tile or -1 for a tile without rows.  relu2: store max(sum, 0)^2.
+PSB_API int psb_gemm_tcgen05_grouped(const void* a, const void* w, void* c, int M, int N, int K, int experts, const void* tile_expert,
+                                     int relu2, int sms, cudaStream_t stream) {
+  if (experts < 1 || !tile_expert) PSB_REFUSE("gemm_tcgen05_grouped: needs the experts and the tiles' experts");
+  if ((long long)experts * N > 0x7fffffffLL) PSB_REFUSE("gemm_tcgen05_grouped: too many rows in the stack of matrices");
+  return launch(a, w, c, M, experts * N, N, K, 0, relu2 ? MODE_RELU2 : MODE_PLAIN, sms, stream, RopeArgs{}, (const int32_t*)tile_expert);
 }
 
 // The projection of an attention layer for many tokens: A W^T with W = [queries; keys; values] [(hq + 2 hkv) D, K] in the

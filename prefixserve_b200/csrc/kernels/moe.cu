@@ -8,8 +8,13 @@
 // s / (sum of the chosen s + 1e-20) * scale.
 //
 // moe_group_kernel (one block): counts the pairs of every expert, lays the experts' rows out one after the other
-// (offsets [E + 1]) and gives every pair its row: row_pair[row] = t * top + slot, pair_row[t * top + slot] = row.
-// Which row of its expert a pair gets does not matter: every row of the products below is computed by itself.
+// (offsets [E + 1]; every expert's first row a multiple of ``pad``, the rows in between belong to nobody) and gives
+// every pair its row: row_pair[row] = t * top + slot (-1: nobody's), pair_row[t * top + slot] = row; tile_expert
+// names the expert of every run of ``pad`` rows (-1 beyond the last).  Which row of its expert a pair gets does not
+// matter: every row of the products below is computed by itself.
+//
+// moe_gather_kernel: the rows of x in that order (zeros for nobody's rows), for the tensor-core product that reads
+// its left operand through a tensor map (gemm_tcgen05.cu, grouped).
 //
 // moe_gemm_kernel: C[row] = act(A[src(row)] . W[e]^T) for the rows of expert e, float32 sums over k in increasing
 // order on the CUDA cores, in 64 x 64 tiles; a row tile never spans two experts (the grid has one row tile more per
@@ -17,6 +22,7 @@
 // ``gather``: A's row is the pair's token (first product) or the row itself (second).  act: none or relu squared.
 //
 // moe_mma_kernel: the same product for bfloat16 operands on the tensor cores (mma.sync m16n8k16, float32 sums).
+// moe_fewrows_kernel: the same for steps with no more than eight rows an expert on average (see there).
 //
 // moe_combine_kernel: out[t] = sum over slots of weight[t, slot] * Y[pair_row[t, slot]]  (+ sigmoid(gate[t]) *
 // shared[t] for a shared expert that every token uses), float32 sums in slot order, rounded to the compute type.
@@ -106,7 +112,7 @@ moe_route_kernel(const float* __restrict__ z, int ldz, const float* __restrict__
 
 __global__ void __launch_bounds__(1024)
 moe_group_kernel(const int32_t* __restrict__ chosen, int32_t* __restrict__ offsets, int32_t* __restrict__ row_pair,
-                 int32_t* __restrict__ pair_row, int pairs, int E) {
+                 int32_t* __restrict__ pair_row, int32_t* __restrict__ tile_expert, int pairs, int E, int pad, int rows_room) {
   __shared__ int count[MAX_EXPERTS];
   __shared__ int cursor[MAX_EXPERTS];
   pdl_trigger();
@@ -124,9 +130,19 @@ moe_group_kernel(const int32_t* __restrict__ chosen, int32_t* __restrict__ offse
     for (int e = 0; e < E; ++e) {
       offsets[e] = at;
       cursor[e] = at;
-      at += count[e];
+      at += (count[e] + pad - 1) / pad * pad;
     }
     offsets[E] = at;
+  }
+  for (int r = threadIdx.x; r < rows_room; r += blockDim.x) row_pair[r] = -1;
+  __syncthreads();
+  if (tile_expert) {
+    for (int tile = threadIdx.x; tile * pad < rows_room; tile += blockDim.x) {
+      int expert = -1;
+      for (int e = 0; e < E; ++e)
+        if (tile * pad >= cursor[e] && tile * pad < cursor[e] + count[e]) expert = e;
+      tile_expert[tile] = expert;
+    }
   }
   __syncthreads();
   for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
@@ -136,6 +152,17 @@ moe_group_kernel(const int32_t* __restrict__ chosen, int32_t* __restrict__ offse
     row_pair[row] = i;
     pair_row[i] = row;
   }
+}
+
+__global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ row_pair,
+                                  __nv_bfloat16* __restrict__ out, int K, int top) {
+  pdl_trigger();
+  pdl_wait();
+  const int row = blockIdx.x;
+  const int pair = row_pair[row];
+  const uint4* src = pair >= 0 ? reinterpret_cast<const uint4*>(x + (size_t)(pair / top) * K) : nullptr;
+  uint4* dst = reinterpret_cast<uint4*>(out + (size_t)row * K);
+  for (int i = threadIdx.x; i < K / 8; i += blockDim.x) dst[i] = src ? src[i] : make_uint4(0, 0, 0, 0);
 }
 
 // Which expert and which of its rows the row tile ``tile`` covers (tiles of ``rows_per_tile`` rows are numbered
@@ -180,7 +207,10 @@ moe_gemm_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TC* __restri
   if (!find_tile(offsets, E, TILE, blockIdx.y, expert, row0, row1)) return;
   const int M = row1 - row0;
   W += (size_t)expert * N * K;
-  for (int i = threadIdx.x; i < TILE; i += blockDim.x) src[i] = i < M ? (gather ? row_pair[row0 + i] / top : row0 + i) : -1;
+  for (int i = threadIdx.x; i < TILE; i += blockDim.x) {
+    const int pair = i < M ? row_pair[row0 + i] : -1;  // -1: a row that belongs to nobody
+    src[i] = pair < 0 ? -1 : (gather ? pair / top : row0 + i);
+  }
   __syncthreads();
   const int n0 = blockIdx.x * TILE;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
@@ -247,7 +277,10 @@ moe_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restr
   if (!find_tile(offsets, E, TILE, blockIdx.y, expert, row0, row1)) return;
   const int M = row1 - row0;
   W += (size_t)expert * N * K;
-  for (int i = threadIdx.x; i < TILE; i += blockDim.x) src[i] = i < M ? (gather ? row_pair[row0 + i] / top : row0 + i) : -1;
+  for (int i = threadIdx.x; i < TILE; i += blockDim.x) {
+    const int pair = i < M ? row_pair[row0 + i] : -1;  // -1: a row that belongs to nobody
+    src[i] = pair < 0 ? -1 : (gather ? pair / top : row0 + i);
+  }
   __syncthreads();
   const int n0 = blockIdx.x * TILE;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -300,6 +333,73 @@ moe_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restr
   }
 }
 
+// A handful of rows per expert (decoding): what matters is that every chosen expert's matrix is read once, as fast as
+// memory gives it.  A block takes one expert and a slab of 32 output columns; the expert's rows (eight at a time) lie in
+// shared memory as bfloat16; a warp takes four of the columns in turn, its lanes along K with 16-byte loads of the
+// weight row, eight sums per column finished by butterflies.  An expert without rows costs its blocks one look-up.
+constexpr int FEW_ROWS = 8, FEW_WARPS = 8, FEW_COLS = 32;
+
+template <typename TC>
+__global__ void __launch_bounds__(FEW_WARPS * 32)
+moe_fewrows_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W, TC* __restrict__ C,
+                   const int32_t* __restrict__ offsets, const int32_t* __restrict__ row_pair, int N, int K, int top, int gather,
+                   int act) {
+  extern __shared__ __align__(16) unsigned char few_smem[];
+  __nv_bfloat16* rows = reinterpret_cast<__nv_bfloat16*>(few_smem);  // [FEW_ROWS][K]
+  pdl_trigger();
+  const int expert = blockIdx.y, n0 = blockIdx.x * FEW_COLS;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const __nv_bfloat16* We = W + (size_t)expert * N * K;
+  pdl_wait();
+  const int row0 = offsets[expert], row1 = offsets[expert + 1];
+  for (int r0 = row0; r0 < row1; r0 += FEW_ROWS) {
+    const int m = min(FEW_ROWS, row1 - r0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < FEW_ROWS * (K / 8); i += blockDim.x) {
+      const int r = i / (K / 8), c = i - r * (K / 8);
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (r < m) {
+        const int pair = row_pair[r0 + r];
+        const int src = pair < 0 ? -1 : (gather ? pair / top : r0 + r);
+        if (src >= 0) v = reinterpret_cast<const uint4*>(A + (size_t)src * K)[c];
+      }
+      reinterpret_cast<uint4*>(rows)[i] = v;
+    }
+    __syncthreads();
+    for (int n = n0 + warp; n < min(N, n0 + FEW_COLS); n += FEW_WARPS) {
+      const uint4* wrow = reinterpret_cast<const uint4*>(We + (size_t)n * K);
+      float acc[FEW_ROWS];
+#pragma unroll
+      for (int r = 0; r < FEW_ROWS; ++r) acc[r] = 0.f;
+      for (int c = lane; c < K / 8; c += 32) {
+        const uint4 wraw = wrow[c];
+        const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wraw);
+        float2 wf[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) wf[j] = __bfloat1622float2(w2[j]);
+#pragma unroll
+        for (int r = 0; r < FEW_ROWS; ++r) {
+          const uint4 araw = reinterpret_cast<const uint4*>(rows + (size_t)r * K)[c];
+          const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&araw);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 af = __bfloat1622float2(a2[j]);
+            acc[r] = fmaf(af.x, wf[j].x, acc[r]);
+            acc[r] = fmaf(af.y, wf[j].y, acc[r]);
+          }
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < FEW_ROWS; ++r) {
+        const float v = warp_sum(acc[r]);
+        if (lane == 0 && r < m) C[(size_t)(r0 + r) * N + n] = from_float<TC>(moe_act(v, act));
+      }
+    }
+  }
+}
+
+PsbPerDevice fewrows_attr[2];
+
 template <typename TY, typename TS, typename TO>
 __global__ void moe_combine_kernel(const TY* __restrict__ Y, const int32_t* __restrict__ pair_row, const float* __restrict__ weight,
                                    const TS* __restrict__ shared, const float* __restrict__ gate, int ldg, TO* __restrict__ out,
@@ -335,15 +435,29 @@ PSB_API int psb_moe_route(const void* z, int ldz, const void* correction, void* 
   return 0;
 }
 
-// (chosen, offsets, row_pair, pair_row, pairs, E, stream)
-PSB_API int psb_moe_group(const void* chosen, void* offsets, void* row_pair, void* pair_row, int pairs, int E, cudaStream_t stream) {
-  if (pairs < 0 || E < 1 || E > MAX_EXPERTS) PSB_REFUSE("moe_group: bad sizes pairs=%d E=%d", pairs, E);
+// (chosen, offsets, row_pair [rows_room], pair_row [pairs], tile_expert [rows_room / pad rounded up] or null, pairs, E, pad,
+//  rows_room, stream); rows_room >= pairs + E * (pad - 1)
+PSB_API int psb_moe_group(const void* chosen, void* offsets, void* row_pair, void* pair_row, void* tile_expert, int pairs, int E,
+                          int pad, int rows_room, cudaStream_t stream) {
+  if (pairs < 0 || E < 1 || E > MAX_EXPERTS || pad < 1) PSB_REFUSE("moe_group: bad sizes pairs=%d E=%d pad=%d", pairs, E, pad);
+  if ((long long)rows_room < (long long)pairs + (long long)E * (pad - 1)) PSB_REFUSE("moe_group: %d rows cannot hold %d pairs of %d experts padded to %d", rows_room, pairs, E, pad);
   psb_launch(moe_group_kernel, dim3(1), dim3(1024), 0, stream, (const int32_t*)chosen, (int32_t*)offsets, (int32_t*)row_pair,
-             (int32_t*)pair_row, pairs, E);
+             (int32_t*)pair_row, (int32_t*)tile_expert, pairs, E, pad, rows_room);
   PSB_LAUNCH_CHECK("moe_group");
   return 0;
 }
 
+// (x bfloat16 [T, K], row_pair [rows], out bfloat16 [rows, K], rows, K, top, stream); K a multiple of 8, 16-byte aligned
+PSB_API int psb_moe_gather(const void* x, const void* row_pair, void* out, int rows, int K, int top, cudaStream_t stream) {
+  if (rows < 0 || K < 8 || K % 8 || top < 1 || (((uintptr_t)x | (uintptr_t)out) & 15)) PSB_REFUSE("moe_gather: needs rows of a multiple of 8 numbers, 16-byte aligned");
+  if (rows == 0) return 0;
+  psb_launch(moe_gather_kernel, dim3(rows), dim3(128), 0, stream, (const __nv_bfloat16*)x, (const int32_t*)row_pair,
+             (__nv_bfloat16*)out, K, top);
+  PSB_LAUNCH_CHECK("moe_gather");
+  return 0;
+}
+
+// ``pairs``: the rows the layout has room for (every expert may have one partly filled tile more than its rows need).
 // (a, a_dtype, w, w_dtype, c, c_dtype, offsets, row_pair, pairs, E, N, K, top, gather, act, stream)
 PSB_API int psb_moe_gemm(const void* a, int a_dtype, const void* w, int w_dtype, void* c, int c_dtype, const void* offsets,
                          const void* row_pair, int pairs, int E, int N, int K, int top, int gather, int act, cudaStream_t stream) {
@@ -353,6 +467,25 @@ PSB_API int psb_moe_gemm(const void* a, int a_dtype, const void* w, int w_dtype,
   const long long row_tiles = (pairs + TILE - 1) / TILE + E;
   if (row_tiles > 65535) PSB_REFUSE("moe_gemm: too many rows for one launch");
   const dim3 grid((N + TILE - 1) / TILE, (unsigned)row_tiles);
+  const size_t few_smem = (size_t)FEW_ROWS * K * sizeof(__nv_bfloat16);
+  if (a_dtype == PSB_BF16 && w_dtype == PSB_BF16 && K % 8 == 0 && (((uintptr_t)a | (uintptr_t)w) & 15) == 0 &&
+      pairs <= FEW_ROWS * E && few_smem <= 192 * 1024 && E <= 65535) {
+    // no more rows than eight an expert on average: stream every used expert's matrix once
+    const dim3 few_grid((N + FEW_COLS - 1) / FEW_COLS, E);
+    PSB_DISPATCH_DTYPE(c_dtype, TC, {
+      auto kernel = moe_fewrows_kernel<TC>;
+      PsbPerDevice& done = fewrows_attr[c_dtype == PSB_F32 ? 0 : 1];
+      if (few_smem > 48 * 1024 && !done.get()) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 192 * 1024) != cudaSuccess)
+          PSB_REFUSE("moe_gemm: cannot raise the shared-memory limit");
+        done.set();
+      }
+      psb_launch(kernel, few_grid, dim3(FEW_WARPS * 32), few_smem, stream, (const __nv_bfloat16*)a, (const __nv_bfloat16*)w, (TC*)c,
+                 (const int32_t*)offsets, (const int32_t*)row_pair, N, K, top, gather, act);
+    });
+    PSB_LAUNCH_CHECK("moe_gemm");
+    return 0;
+  }
   if (a_dtype == PSB_BF16 && w_dtype == PSB_BF16 && K % 8 == 0 && (((uintptr_t)a | (uintptr_t)w) & 15) == 0) {
     PSB_DISPATCH_DTYPE(c_dtype, TC, {
       psb_launch(moe_mma_kernel<TC>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)a, (const __nv_bfloat16*)w, (TC*)c,

@@ -191,7 +191,7 @@ class Engine:
         for b in sorted(set(int(x) for x in batch_sizes)):
             if b < 1 or b > self.cfg.max_num_seqs:
                 continue
-            if self.cache.slots.num_free < b or self.cache.free_pages(0) < b:
+            if self.cache.slots.num_free < b or (self.cache.groups and self.cache.free_pages(0) < b):
                 break
             wanted = [k for k in self.runner.length_classes if not self.runner.has_decode_graph(b, k)]
             if not wanted:

@@ -750,7 +750,8 @@ def norm_add_norm(h: torch.Tensor, y: torch.Tensor, gain_post: torch.Tensor, eps
     return x
 
 
-BIASED_TILE_MIN_TOKENS = 16  # portions from this many tokens on go to the kernel that stages keys for a tile of tokens
+BIASED_TILE_MIN_TOKENS = 16  # portions from this many tokens on go to the kernels that stage keys for a tile of tokens
+BIASED_MMA = True            # ... the tensor-core one where the sizes allow (multiples of 8 up to 128), else the CUDA-core one
 
 
 def biased_attention(qkv: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, ctx, *, num_heads: int, num_kv_heads: int,
@@ -783,10 +784,11 @@ def biased_attention(qkv: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, c
     win, chk = int(window or 0), int(chunk or 0)
     # Portions of a bfloat16 step go tile by tile; what is left (single tokens, short portions) walks its keys.  Which
     # kernel a token gets depends on the length of its portion only (decided on the device from the item offsets, so
-    # the launches have the same shape whatever the step holds); both give the same sums.
+    # the launches have the same shape whatever the step holds).
     item_start = _i32(ctx.item_start, "item offsets")
-    tiled = (qkv.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16 and ctx.max_new_tokens >= BIASED_TILE_MIN_TOKENS
-             and bool(lib().psb_attention_biased_tile_supported(num_heads, num_kv_heads, dim, vdim)))
+    long_portions = qkv.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16 and ctx.max_new_tokens >= BIASED_TILE_MIN_TOKENS
+    on_tensor_cores = long_portions and BIASED_MMA and bool(lib().psb_attention_biased_mma_supported(num_heads, num_kv_heads, dim, vdim))
+    tiled = long_portions and (on_tensor_cores or bool(lib().psb_attention_biased_tile_supported(num_heads, num_kv_heads, dim, vdim)))
     if not (tiled and ctx.num_items == 1):  # a step that is one long portion has nothing for the walking kernel
         check(lib().psb_attention_biased(q.data_ptr(), _code(q, "queries"), kv.data_ptr(), _code(kv, "cache entry"),
                                          table.data_ptr(), table.shape[1], positions.data_ptr(), token_item.data_ptr(),
@@ -794,10 +796,11 @@ def biased_attention(qkv: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, c
                                          page_size, win, chk, reach, float(scale), item_start.data_ptr(),
                                          BIASED_TILE_MIN_TOKENS if tiled else 0, _stream()), "attention_biased")
     if tiled:
-        check(lib().psb_attention_biased_tiles(q.data_ptr(), kv.data_ptr(), table.data_ptr(), table.shape[1], positions.data_ptr(),
-                                               item_start.data_ptr(), ctx.num_items, t, BIASED_TILE_MIN_TOKENS, _ptr(bias),
-                                               _ptr(sink), out.data_ptr(), num_heads, num_kv_heads, dim, vdim, page_size, win,
-                                               chk, reach, float(scale), _stream()), "attention_biased_tiles")
+        entry = lib().psb_attention_biased_mma if on_tensor_cores else lib().psb_attention_biased_tiles
+        check(entry(q.data_ptr(), kv.data_ptr(), table.data_ptr(), table.shape[1], positions.data_ptr(), item_start.data_ptr(),
+                    ctx.num_items, t, BIASED_TILE_MIN_TOKENS, _ptr(bias), _ptr(sink), out.data_ptr(), num_heads, num_kv_heads, dim,
+                    vdim, page_size, win, chk, reach, float(scale), _stream()),
+              "attention_biased_mma" if on_tensor_cores else "attention_biased_tiles")
     return out
 
 
@@ -861,6 +864,8 @@ def moe_route(z: torch.Tensor, correction: torch.Tensor | None, *, experts: int,
 
 
 MOE_ACTIVATIONS = {None: 0, "relu2": 1}
+MOE_TCGEN05 = True            # bfloat16 experts on the grouped tcgen05 product
+MOE_TCGEN05_MIN_PAIRS = 256   # with fewer (token, expert) pairs in a step the 64-row tiles of the mma.sync kernel waste less
 
 
 def moe_experts(x: torch.Tensor, chosen: torch.Tensor, weight: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, *,
@@ -878,18 +883,37 @@ def moe_experts(x: torch.Tensor, chosen: torch.Tensor, weight: torch.Tensor, w_u
     if activation not in MOE_ACTIVATIONS:
         raise KernelError(f"experts: activation {activation!r} is not built (one of {sorted(k for k in MOE_ACTIVATIONS if k)})")
     dev, pairs = x.device, t * top
+    # bfloat16 with rows the tensor map takes: the experts' rows start at multiples of 128 and both products run on the
+    # tcgen05 kernel, every 128-row tile against its own expert's matrix; otherwise tiles of 64 rows on mma.sync or FFMA
+    grouped = (MOE_TCGEN05 and x.dtype == torch.bfloat16 and w_up.dtype == torch.bfloat16 and w_down.dtype == torch.bfloat16
+               and h % 8 == 0 and ff % 8 == 0 and pairs >= MOE_TCGEN05_MIN_PAIRS)
+    pad = 128 if grouped else 1
+    room = -(-(pairs + e * (pad - 1)) // pad) * pad
     offsets = torch.empty((e + 1,), dtype=torch.int32, device=dev)
-    row_pair = torch.empty((max(pairs, 1),), dtype=torch.int32, device=dev)
+    row_pair = torch.empty((max(room, 1),), dtype=torch.int32, device=dev)
     pair_row = torch.empty((max(pairs, 1),), dtype=torch.int32, device=dev)
-    check(lib().psb_moe_group(chosen.data_ptr(), offsets.data_ptr(), row_pair.data_ptr(), pair_row.data_ptr(), pairs, e, _stream()),
-          "moe_group")
-    mid = torch.empty((pairs, ff), dtype=x.dtype, device=dev)
-    check(lib().psb_moe_gemm(x.data_ptr(), _code(x, "expert input"), w_up.data_ptr(), _code(w_up, "expert up matrices"), mid.data_ptr(),
-                             _code(mid, "expert activations"), offsets.data_ptr(), row_pair.data_ptr(), pairs, e, ff, h, top, 1,
-                             MOE_ACTIVATIONS[activation], _stream()), "moe_gemm")
-    y = torch.empty((pairs, h), dtype=torch.float32, device=dev)
-    check(lib().psb_moe_gemm(mid.data_ptr(), _code(mid, "expert activations"), w_down.data_ptr(), _code(w_down, "expert down matrices"),
-                             y.data_ptr(), F32, offsets.data_ptr(), row_pair.data_ptr(), pairs, e, h, ff, top, 0, 0, _stream()), "moe_gemm")
+    tile_expert = torch.empty((room // pad,), dtype=torch.int32, device=dev) if grouped else None
+    check(lib().psb_moe_group(chosen.data_ptr(), offsets.data_ptr(), row_pair.data_ptr(), pair_row.data_ptr(), _ptr(tile_expert),
+                              pairs, e, pad, room, _stream()), "moe_group")
+    if grouped:
+        from .tensorcore import _sms
+        sms = _sms(dev)
+        rows = torch.empty((room, h), dtype=torch.bfloat16, device=dev)
+        check(lib().psb_moe_gather(x.data_ptr(), row_pair.data_ptr(), rows.data_ptr(), room, h, top, _stream()), "moe_gather")
+        mid = torch.empty((room, ff), dtype=torch.bfloat16, device=dev)
+        check(lib().psb_gemm_tcgen05_grouped(rows.data_ptr(), w_up.data_ptr(), mid.data_ptr(), room, ff, h, e, tile_expert.data_ptr(),
+                                             MOE_ACTIVATIONS[activation], sms, _stream()), "gemm_tcgen05_grouped")
+        y = torch.empty((room, h), dtype=torch.bfloat16, device=dev)
+        check(lib().psb_gemm_tcgen05_grouped(mid.data_ptr(), w_down.data_ptr(), y.data_ptr(), room, h, ff, e, tile_expert.data_ptr(),
+                                             0, sms, _stream()), "gemm_tcgen05_grouped")
+    else:
+        mid = torch.empty((room, ff), dtype=x.dtype, device=dev)
+        check(lib().psb_moe_gemm(x.data_ptr(), _code(x, "expert input"), w_up.data_ptr(), _code(w_up, "expert up matrices"), mid.data_ptr(),
+                                 _code(mid, "expert activations"), offsets.data_ptr(), row_pair.data_ptr(), room, e, ff, h, top, 1,
+                                 MOE_ACTIVATIONS[activation], _stream()), "moe_gemm")
+        y = torch.empty((room, h), dtype=torch.float32, device=dev)
+        check(lib().psb_moe_gemm(mid.data_ptr(), _code(mid, "expert activations"), w_down.data_ptr(), _code(w_down, "expert down matrices"),
+                                 y.data_ptr(), F32, offsets.data_ptr(), row_pair.data_ptr(), room, e, h, ff, top, 0, 0, _stream()), "moe_gemm")
     out = torch.empty((t, h), dtype=out_dtype or x.dtype, device=dev)
     ldg = 0
     if shared is not None:
@@ -900,7 +924,7 @@ def moe_experts(x: torch.Tensor, chosen: torch.Tensor, weight: torch.Tensor, w_u
             if shared_gate.dtype != torch.float32 or shared_gate.shape[0] != t or not shared_gate.is_cuda:
                 raise KernelError("experts: the shared expert's gate must be a float32 column on the device")
             ldg = shared_gate.stride(0)
-    check(lib().psb_moe_combine(y.data_ptr(), F32, pair_row.data_ptr(), weight.data_ptr(), _ptr(shared),
+    check(lib().psb_moe_combine(y.data_ptr(), _code(y, "experts' outputs"), pair_row.data_ptr(), weight.data_ptr(), _ptr(shared),
                                 _code(shared, "shared expert output") if shared is not None else F32,
                                 _ptr(shared_gate) if shared is not None else None, ldg, out.data_ptr(), _code(out, "experts' sum"),
                                 t, h, top, _stream()), "moe_combine")

@@ -167,6 +167,8 @@ _SIGNATURES: dict[str, list] = {
     # (q, kv, table, table_width, positions, item_start, items, T, min_tokens, bias, sink, out, hq, hkv, dim, vdim,
     #  page_size, window, chunk, reach, scale, stream)
     "psb_attention_biased_tiles": [P, P, P, I, P, P, I, I, I, P, P, P, I, I, I, I, I, I, I, I, F, P],
+    "psb_attention_biased_mma_supported": [I, I, I, I],
+    "psb_attention_biased_mma": [P, P, P, I, P, P, I, I, I, P, P, P, I, I, I, I, I, I, I, I, F, P],
     "psb_delta_max_taps": [],
     # (proj, dtype, ba, taps, a_log, dt_bias, state, positions, token_item, item_start, slots, qkv_out, bd_out, T, G, H, dim,
     #  vdim, K, num_slots, slot_floats, stream)
@@ -177,8 +179,12 @@ _SIGNATURES: dict[str, list] = {
     "psb_delta_finish": [P, P, I, P, P, I, I, I, I, I, F, P],
     # (z, ldz, correction, chosen, weight, T, E, top, groups, keep, scale, stream)
     "psb_moe_route": [P, I, P, P, P, I, I, I, I, I, F, P],
-    # (chosen, offsets, row_pair, pair_row, pairs, E, stream)
-    "psb_moe_group": [P, P, P, P, I, I, P],
+    # (chosen, offsets, row_pair, pair_row, tile_expert, pairs, E, pad, rows_room, stream)
+    "psb_moe_group": [P, P, P, P, P, I, I, I, I, P],
+    # (x, row_pair, out, rows, K, top, stream)
+    "psb_moe_gather": [P, P, P, I, I, I, P],
+    # (a, w, c, M, N, K, experts, tile_expert, relu2, sms, stream)
+    "psb_gemm_tcgen05_grouped": [P, P, P, I, I, I, I, P, I, I, P],
     # (a, a_dtype, w, w_dtype, c, c_dtype, offsets, row_pair, pairs, E, N, K, top, gather, act, stream)
     "psb_moe_gemm": [P, I, P, I, P, I, P, P, I, I, I, I, I, I, I, P],
     # (y, y_dtype, pair_row, weight, shared, shared_dtype, gate, ldg, out, out_dtype, T, H, top, stream)

@@ -6,7 +6,7 @@ is the sum of its two largest choice scores and only experts of the ``keep`` bes
 of the chosen experts are their s divided by the sum of those (+ 1e-20), times ``scale``.  A shared expert of the same
 form (``shared_size``) may run for every token; its output is multiplied by sigmoid(w_sg . x), one number per token.
 
-The router and the shared expert's gate are one float32 product.  The chosen (token, expert) pairs are grouped by
+The router and the shared expert's gate are one product with float32 sums and float32 output.  The chosen (token, expert) pairs are grouped by
 expert on the device and every expert multiplies its own rows only; nothing of the routing comes back to the host.
 """
 
@@ -64,10 +64,11 @@ class RoutedExperts(FeedForward):
         dtype = torch.float32 if any(p.dtype == torch.float32 for p in ups + downs) else ups[0].dtype
         self.w_up = torch.stack([p.to(dtype) for p in ups]).contiguous()       # [E, ff, H]
         self.w_down = torch.stack([p.to(dtype) for p in downs]).contiguous()   # [E, H, ff]
-        rows = [tensors["router"].to(device=device, dtype=torch.float32)]
-        if self.shared_gated:
-            rows.append(tensors["shared.gate"].to(device=device, dtype=torch.float32))
-        self.w_router = torch.cat(rows, dim=0).contiguous()  # float32: the router's product runs in 32-bit on both paths
+        # The router's rows (and the shared expert's gate, one more row) keep the type they arrive in: bfloat16 weights
+        # against bfloat16 rows multiply exactly and are summed in float32, and the logits leave the product as float32.
+        rows = [tensors["router"]] + ([tensors["shared.gate"]] if self.shared_gated else [])
+        dtype = torch.float32 if any(r.dtype == torch.float32 for r in rows) else rows[0].dtype
+        self.w_router = torch.cat([r.to(dtype) for r in rows], dim=0).contiguous()
         if self.has_correction:
             self.correction = tensors["correction"].to(device=device, dtype=torch.float32).contiguous()
         if self.shared_size is not None:

@@ -68,6 +68,13 @@ CONFIGS = {
         layer("attention", attention(heads=5, kv_heads=1, dim=4, vdim=3, scale=0.5, bias_max=300, chunk=64, rows=32), None),
         layer("delta", delta(heads=2, kv_heads=1, dim=33, vdim=7, conv=5), moe(experts=5, top=1, ff=6, groups=5, keep=2, shared=3)),
     ], vocab=131, width=40, eps=3e-6, scale=5.5),
+    # nothing routed: every bfloat16 row can be held to the oracle (no token that rounding could send to another expert)
+    "dense": config([
+        layer("attention", attention(heads=6, kv_heads=3, dim=5, vdim=9, scale=0.35, bias_max=40, chunk=29, rows=9), dense(40)),
+        layer("delta", delta(heads=4, kv_heads=1, dim=12, vdim=6, conv=3), None),
+        layer("attention", attention(heads=2, kv_heads=1, dim=24, vdim=8, scale=0.2, bias_max=16, chunk=None, rows=7), dense(33)),
+        layer("delta", delta(heads=2, kv_heads=2, dim=10, vdim=20, conv=4), dense(64)),
+    ], vocab=97, width=48, eps=1e-5, scale=2.0),
     # sizes in the multiples the tensor-core products take (rows of 8 and more elements, 16-byte aligned)
     "wide": config([
         layer("delta", delta(heads=4, kv_heads=2, dim=32, vdim=48, conv=4), moe(experts=8, top=2, ff=64, groups=2, keep=1, shared=96)),
