@@ -14,7 +14,7 @@
 //
 // delta_rule_kernel: per request and head, token by token,
 //     S <- decay S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q,
-// so the read-out sees the current token's write.  The columns of S (one per value channel) never meet: R lanes of
+// so the read-out sees the current token's write (computed as decay (S_old^T q) + (q.k) u, which is the same).  The columns of S (one per value channel) never meet: R lanes of
 // a warp hold one column between them (dim / R numbers each, in registers), so a warp carries 32 / R columns, and
 // the two dot products of a token are finished by a butterfly among the R lanes.  The order of every sum depends on
 // R and dim only, never on the batch.  What a run of tokens brings is staged in shared memory for the whole block, one
@@ -107,6 +107,10 @@ __device__ __forceinline__ void copy_async4(float* dst, const float* src) {
   const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
 }
+__device__ __forceinline__ void copy_async16(float* dst, const float* src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
 __device__ __forceinline__ void copy_async_wait() {
   asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
 }
@@ -114,15 +118,21 @@ __device__ __forceinline__ void copy_async_wait() {
 // PER: numbers of a column one lane holds; R: lanes per column.  R * PER >= dim.  What the tokens of a stage bring
 // (queries, keys, the block's value columns, beta, decay) is copied into shared memory one stage ahead of the
 // arithmetic (cp.async into the other of two buffers), so the chain from token to token never waits for memory.
+//
+// The chain itself is kept short: with S the state before the token, the three sums k.S, q.S (per column) and q.k are
+// finished by one butterfly, and then
+//     u = beta (v - dec k.S),   o = dec q.S + (q.k) u,   S <- dec S + k u^T,
+// which is the read-out of the updated state written so that it does not wait for the update.
 template <typename T, int PER, int R>
 __global__ void __launch_bounds__(RULE_WARPS * 32)
 delta_rule_kernel(const float* __restrict__ qkv, const float* __restrict__ bd, const T* __restrict__ proj,
                   float* __restrict__ state, const int32_t* __restrict__ item_start, const int32_t* __restrict__ slots,
                   float* __restrict__ o, int G, int H, int dim, int vdim, int K, int num_slots, size_t slot_floats,
                   int stage_tokens) {
-  extern __shared__ float staged[];  // [2][stage_tokens][W]
+  extern __shared__ __align__(16) float staged[];  // [2][stage_tokens][W]
   constexpr int COLS = 32 / R;  // columns a warp holds
-  constexpr int RP = R * PER, BC = RULE_WARPS * COLS, W = 2 * RP + BC + 2;
+  constexpr int RP = R * PER, BC = RULE_WARPS * COLS, W = (2 * RP + BC + 2 + 3) / 4 * 4;
+  static_assert(RP % 4 == 0, "queries and keys of a token start on 16 bytes");
   pdl_trigger();
   const int C = 2 * G * dim + H * vdim, P = C + H * vdim;
   const int h = blockIdx.y, item = blockIdx.z;
@@ -132,6 +142,8 @@ delta_rule_kernel(const float* __restrict__ qkv, const float* __restrict__ bd, c
   const int col0 = blockIdx.x * BC, in_block = warp * COLS + lane / R;
   const int col = col0 + in_block;
   const bool live = col < vdim;
+  // 16-byte copies of queries and keys need their rows on 16 bytes in the [T, C] array
+  const bool wide = dim % 4 == 0 && C % 4 == 0 && (((uintptr_t)qkv) & 15) == 0;
   pdl_wait();
   const int t0 = item_start[item], t1 = item_start[item + 1];
   int slot = slots[item];
@@ -141,20 +153,29 @@ delta_rule_kernel(const float* __restrict__ qkv, const float* __restrict__ bd, c
 
   auto stage = [&](int ts, float* buf) {  // tokens ts .. ts + stage_tokens - 1 (those before t1) into buf
     const int n = min(stage_tokens, t1 - ts);
-    for (int i = threadIdx.x; i < n * W; i += blockDim.x) {
-      const int tok = i / W, e = i - tok * W;
-      const float* row = qkv + (size_t)(ts + tok) * C;
-      const float* src = nullptr;
-      if (e < 2 * RP) {
+    if (wide) {
+      constexpr int PIECES = 2 * RP / 4;  // 16-byte pieces of a token's queries and keys
+      for (int i = threadIdx.x; i < n * PIECES; i += blockDim.x) {
+        const int tok = i / PIECES, e = (i - tok * PIECES) * 4;
         const int which = e / RP, d = e - which * RP;
-        if (d < dim) src = row + (size_t)which * G * dim + g * dim + d;
-      } else if (e < 2 * RP + BC) {
-        if (col0 + e - 2 * RP < vdim) src = row + 2 * G * dim + h * vdim + col0 + e - 2 * RP;
-      } else {
-        src = bd + (size_t)(ts + tok) * 2 * H + (e - 2 * RP - BC) * H + h;
+        float* dst = buf + tok * W + e;
+        if (d < dim) copy_async16(dst, qkv + (size_t)(ts + tok) * C + (size_t)which * G * dim + g * dim + d);
+        else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
       }
-      if (src) copy_async4(buf + i, src);
-      else buf[i] = 0.f;
+    } else {
+      for (int i = threadIdx.x; i < n * 2 * RP; i += blockDim.x) {
+        const int tok = i / (2 * RP), e = i - tok * 2 * RP;
+        const int which = e / RP, d = e - which * RP;
+        if (d < dim) copy_async4(buf + tok * W + e, qkv + (size_t)(ts + tok) * C + (size_t)which * G * dim + g * dim + d);
+        else buf[tok * W + e] = 0.f;
+      }
+    }
+    for (int i = threadIdx.x; i < n * (BC + 2); i += blockDim.x) {
+      const int tok = i / (BC + 2), e = i - tok * (BC + 2);
+      float* dst = buf + tok * W + 2 * RP + e;
+      if (e >= BC) copy_async4(dst, bd + (size_t)(ts + tok) * 2 * H + (e - BC) * H + h);
+      else if (col0 + e < vdim) copy_async4(dst, qkv + (size_t)(ts + tok) * C + 2 * G * dim + h * vdim + col0 + e);
+      else *dst = 0.f;
     }
   };
 
@@ -174,38 +195,47 @@ delta_rule_kernel(const float* __restrict__ qkv, const float* __restrict__ bd, c
     const float* buf = staged + (size_t)which_buf * stage_tokens * W;
     for (int i = 0; i < n; ++i) {
       const float* tokrow = buf + i * W;
-      const float* qq = tokrow + r * PER;
-      const float* kk = tokrow + RP + r * PER;
+      float qq[PER], kk[PER];
+      if constexpr (PER % 4 == 0) {
+#pragma unroll
+        for (int e = 0; e < PER; e += 4) {
+          const float4 a = *reinterpret_cast<const float4*>(tokrow + r * PER + e);
+          const float4 b4 = *reinterpret_cast<const float4*>(tokrow + RP + r * PER + e);
+          qq[e] = a.x; qq[e + 1] = a.y; qq[e + 2] = a.z; qq[e + 3] = a.w;
+          kk[e] = b4.x; kk[e + 1] = b4.y; kk[e + 2] = b4.z; kk[e + 3] = b4.w;
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < PER; ++e) {
+          qq[e] = tokrow[r * PER + e];
+          kk[e] = tokrow[RP + r * PER + e];
+        }
+      }
       const float v = tokrow[2 * RP + in_block];
       const float beta = tokrow[2 * RP + BC], dec = tokrow[2 * RP + BC + 1];
-      float kd0 = 0.f, kd1 = 0.f;
+      float ks0 = 0.f, ks1 = 0.f, qs0 = 0.f, qs1 = 0.f, qk = 0.f;
 #pragma unroll
       for (int e = 0; e < PER; e += 2) {
-        s[e] *= dec;
-        kd0 = fmaf(kk[e], s[e], kd0);
+        ks0 = fmaf(kk[e], s[e], ks0);
+        qs0 = fmaf(qq[e], s[e], qs0);
+        qk = fmaf(qq[e], kk[e], qk);
         if (e + 1 < PER) {
-          s[e + 1] *= dec;
-          kd1 = fmaf(kk[e + 1], s[e + 1], kd1);
+          ks1 = fmaf(kk[e + 1], s[e + 1], ks1);
+          qs1 = fmaf(qq[e + 1], s[e + 1], qs1);
+          qk = fmaf(qq[e + 1], kk[e + 1], qk);
         }
       }
-      float kd = kd0 + kd1;
+      float ksum = ks0 + ks1, qsum = qs0 + qs1;
 #pragma unroll
-      for (int off = 1; off < R; off <<= 1) kd += __shfl_xor_sync(0xffffffffu, kd, off);
-      const float u = beta * (v - kd);
-      float od0 = 0.f, od1 = 0.f;
-#pragma unroll
-      for (int e = 0; e < PER; e += 2) {
-        s[e] = fmaf(kk[e], u, s[e]);
-        od0 = fmaf(qq[e], s[e], od0);
-        if (e + 1 < PER) {
-          s[e + 1] = fmaf(kk[e + 1], u, s[e + 1]);
-          od1 = fmaf(qq[e + 1], s[e + 1], od1);
-        }
+      for (int off = 1; off < R; off <<= 1) {
+        ksum += __shfl_xor_sync(0xffffffffu, ksum, off);
+        qsum += __shfl_xor_sync(0xffffffffu, qsum, off);
+        qk += __shfl_xor_sync(0xffffffffu, qk, off);
       }
-      float od = od0 + od1;
+      const float u = beta * (v - dec * ksum);
 #pragma unroll
-      for (int off = 1; off < R; off <<= 1) od += __shfl_xor_sync(0xffffffffu, od, off);
-      if (live && r == 0) o[((size_t)(ts + i) * H + h) * vdim + col] = od;
+      for (int e = 0; e < PER; ++e) s[e] = fmaf(kk[e], u, dec * s[e]);
+      if (live && r == 0) o[((size_t)(ts + i) * H + h) * vdim + col] = fmaf(qk, u, dec * qsum);
     }
   }
 #pragma unroll
@@ -259,7 +289,7 @@ template <typename T, int PER, int R>
 void launch_rule(dim3 grid, cudaStream_t stream, const float* qkv, const float* bd, const T* proj, float* state,
                  const int32_t* item_start, const int32_t* slots, float* o, int G, int H, int dim, int vdim, int K,
                  int num_slots, size_t slot_floats) {
-  constexpr int W = 2 * R * PER + RULE_WARPS * (32 / R) + 2;
+  constexpr int W = (2 * R * PER + RULE_WARPS * (32 / R) + 2 + 3) / 4 * 4;
   // two buffers within the 48 KB a kernel has without asking: 16 tokens a stage for keys up to 128 numbers, 4 beyond
   const int stage_tokens = 2 * 16 * W * (int)sizeof(float) <= 48 * 1024 ? 16 : 4;
   static_assert(2 * 4 * W * sizeof(float) <= 48 * 1024, "a stage of four tokens fits the default shared memory twice");
