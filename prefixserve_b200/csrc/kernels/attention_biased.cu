@@ -341,6 +341,7 @@ attention_biased_tile_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
 // scale, bias, masks and the online softmax (started from the sink) are applied in float32; the weights enter the
 // second product as the sum of two bfloat16 numbers (p = hi + lo, two instructions), so they keep 16 bits.
 constexpr int MMA_ROWS = 64, MMA_KEYS = 64;
+constexpr int MMA_BIAS = 2048;  // distances whose bias a block keeps in shared memory
 
 __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -367,6 +368,7 @@ attention_biased_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
   constexpr int KS = D + 8, VS = MMA_KEYS + 8;  // row pitches that keep the fragment loads off each other's banks
   __shared__ __align__(16) __nv_bfloat16 ks[MMA_KEYS * KS];   // keys [key][d]; first the tile's queries [row][d]
   __shared__ __align__(16) __nv_bfloat16 vt[V * VS];          // values transposed [v][key]
+  __shared__ float near_bias[MMA_BIAS];                       // the head's bias for the nearest distances
   pdl_trigger();
   pdl_wait();
   int item = -1, t0 = 0;
@@ -417,33 +419,52 @@ attention_biased_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
 #pragma unroll
   for (int i = 0; i < V / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   const float* brow = bias ? bias + (size_t)h * reach : nullptr;
+  if (brow)
+    for (int i = threadIdx.x; i < min(reach, MMA_BIAS); i += 128) near_bias[i] = brow[i];  // visible after the loop's first barrier
 
   int lo_tile = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
   if (chunk > 0) lo_tile = max(lo_tile, (p_first / chunk) * chunk);
   for (int base = lo_tile & ~(MMA_KEYS - 1); base <= p_last; base += MMA_KEYS) {
     __syncthreads();  // everybody has its query fragments (first round) or is done with the last block
-    for (int i = threadIdx.x; i < MMA_KEYS * (D / 8); i += blockDim.x) {
+    // every thread asks for all its pieces of the block (page ids first, then the rows) before it stores any
+    constexpr int KPIECES = MMA_KEYS * (D / 8) / 128, VPIECES = MMA_KEYS * (V / 8) / 128;
+    uint4 kreg[KPIECES], vreg[VPIECES];
+#pragma unroll
+    for (int u = 0; u < KPIECES; ++u) {
+      const int i = threadIdx.x + u * 128;
       const int j = i / (D / 8), c = (i - j * (D / 8)) * 8;
       const int key = base + j;
-      uint4 v = make_uint4(0, 0, 0, 0);
+      kreg[u] = make_uint4(0, 0, 0, 0);
       if (key >= lo_tile && key <= p_last && c < dim)
-        v = *reinterpret_cast<const uint4*>(kv + (size_t)pages[key / page_size] * page_elems + (size_t)g * head_stride +
-                                            (size_t)(key % page_size) * rw + c);
-      *reinterpret_cast<uint4*>(&ks[j * KS + c]) = v;
+        kreg[u] = *reinterpret_cast<const uint4*>(kv + (size_t)pages[key / page_size] * page_elems + (size_t)g * head_stride +
+                                                  (size_t)(key % page_size) * rw + c);
     }
-    for (int i = threadIdx.x; i < MMA_KEYS * (V / 8); i += blockDim.x) {
+#pragma unroll
+    for (int u = 0; u < VPIECES; ++u) {
+      const int i = threadIdx.x + u * 128;
       const int j = i % MMA_KEYS, c = (i / MMA_KEYS) * 8;  // neighbouring lanes: neighbouring keys, the same eight value channels
       const int key = base + j;
-      uint4 v = make_uint4(0, 0, 0, 0);
+      vreg[u] = make_uint4(0, 0, 0, 0);
       if (key >= lo_tile && key <= p_last && c < vdim)
-        v = *reinterpret_cast<const uint4*>(kv + (size_t)pages[key / page_size] * page_elems + (size_t)g * head_stride +
-                                            (size_t)(key % page_size) * rw + dim + c);
-      const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v);
+        vreg[u] = *reinterpret_cast<const uint4*>(kv + (size_t)pages[key / page_size] * page_elems + (size_t)g * head_stride +
+                                                  (size_t)(key % page_size) * rw + dim + c);
+    }
+#pragma unroll
+    for (int u = 0; u < KPIECES; ++u) {
+      const int i = threadIdx.x + u * 128;
+      const int j = i / (D / 8), c = (i - j * (D / 8)) * 8;
+      *reinterpret_cast<uint4*>(&ks[j * KS + c]) = kreg[u];
+    }
+#pragma unroll
+    for (int u = 0; u < VPIECES; ++u) {
+      const int i = threadIdx.x + u * 128;
+      const int j = i % MMA_KEYS, c = (i / MMA_KEYS) * 8;
+      const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&vreg[u]);
 #pragma unroll
       for (int k = 0; k < 8; ++k) vt[(c + k) * VS + j] = e[k];
     }
     __syncthreads();
-    if (base > p_first + warp * 16 + 15) continue;  // all of this warp's rows lie before the block (uniform in the warp)
+    if (warp * 16 >= nt || base > p_first + warp * 16 + 15) continue;  // no rows, or all of them before the block (uniform in the warp)
     float sc[MMA_KEYS / 8][4];
 #pragma unroll
     for (int n = 0; n < MMA_KEYS / 8; ++n) {
@@ -464,7 +485,10 @@ attention_biased_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
         float v = -INFINITY;
         if (key <= pos[r] && key >= low[r]) {
           v = sc[n][e] * scale;
-          if (brow) v += brow[min(pos[r] - key, reach - 1)];
+          if (brow) {
+            const int far = min(pos[r] - key, reach - 1);
+            v += far < MMA_BIAS ? near_bias[far] : brow[far];
+          }
         }
         sc[n][e] = v;
         top[r] = fmaxf(top[r], v);

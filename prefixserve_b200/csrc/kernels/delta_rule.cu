@@ -327,13 +327,13 @@ PSB_API int psb_delta_prepare(const void* proj, int dtype, const void* ba, const
 
 // (qkv, bd, proj, dtype, state, item_start, slots, o_out, items, G, H, dim, vdim, K, num_slots, slot_floats, lanes, stream)
 // ``lanes``: lanes of a warp that share a column of the state (4: a warp reads whole sectors of the state, for steps
-// of single tokens; 16: short chains per token, for long portions).
+// of single tokens; 16 or 32: short chains per token and more warps, for long portions).
 PSB_API int psb_delta_rule(const void* qkv, const void* bd, const void* proj, int dtype, void* state, const void* item_start,
                            const void* slots, void* o, int items, int G, int H, int dim, int vdim, int K, int num_slots,
                            long long slot_floats, int lanes, cudaStream_t stream) {
   if (items < 0 || G < 1 || H < 1 || H % G || dim < 1 || vdim < 1) PSB_REFUSE("delta_rule: bad sizes G=%d H=%d dim=%d vdim=%d", G, H, dim, vdim);
   if (K < 1 || K > MAX_TAPS) PSB_REFUSE("delta_rule: %d taps are outside [1, %d]", K, MAX_TAPS);
-  if (lanes != 4 && lanes != 16) PSB_REFUSE("delta_rule: %d lanes a column is not built (4 or 16)", lanes);
+  if (lanes != 4 && lanes != 16 && lanes != 32) PSB_REFUSE("delta_rule: %d lanes a column is not built (4, 16 or 32)", lanes);
   if (dim > 64 * lanes) PSB_REFUSE("delta_rule: key size %d exceeds %d", dim, 64 * lanes);
   if (H > 65535 || items > 65535) PSB_REFUSE("delta_rule: too many heads or requests for one launch");
   if (items == 0) return 0;
@@ -351,11 +351,16 @@ PSB_API int psb_delta_rule(const void* qkv, const void* bd, const void* proj, in
       else if (per <= 16) RULE(16, 4);
       else if (per <= 32) RULE(32, 4);
       else RULE(64, 4);
-    } else {
+    } else if (lanes == 16) {
       if (per <= 2) RULE(2, 16);
       else if (per <= 4) RULE(4, 16);
       else if (per <= 8) RULE(8, 16);
       else RULE(16, 16);
+    } else {
+      if (per <= 1) RULE(1, 32);
+      else if (per <= 2) RULE(2, 32);
+      else if (per <= 4) RULE(4, 32);
+      else RULE(8, 32);
     }
   });
 #undef RULE

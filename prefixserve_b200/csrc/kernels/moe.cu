@@ -22,7 +22,7 @@
 // ``gather``: A's row is the pair's token (first product) or the row itself (second).  act: none or relu squared.
 //
 // moe_mma_kernel: the same product for bfloat16 operands on the tensor cores (mma.sync m16n8k16, float32 sums).
-// moe_fewrows_kernel: the same for steps with no more than eight rows an expert on average (see there).
+// moe_fewrows_kernel: the same for steps with no more than four rows an expert on average (see there).
 //
 // moe_combine_kernel: out[t] = sum over slots of weight[t, slot] * Y[pair_row[t, slot]]  (+ sigmoid(gate[t]) *
 // shared[t] for a shared expert that every token uses), float32 sums in slot order, rounded to the compute type.
@@ -334,13 +334,13 @@ moe_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restr
 }
 
 // A handful of rows per expert (decoding): what matters is that every chosen expert's matrix is read once, as fast as
-// memory gives it.  A block takes one expert and a slab of 32 output columns; the expert's rows (eight at a time) lie in
+// memory gives it.  A block takes one expert and a slab of 32 output columns; the expert's rows (four at a time) lie in
 // shared memory as bfloat16; a warp takes four of the columns in turn, its lanes along K with 16-byte loads of the
-// weight row, eight sums per column finished by butterflies.  An expert without rows costs its blocks one look-up.
-constexpr int FEW_ROWS = 8, FEW_WARPS = 8, FEW_COLS = 32;
+// weight rows, four sums per column finished by butterflies.  An expert without rows costs its blocks one look-up.
+constexpr int FEW_ROWS = 4, FEW_WARPS = 8, FEW_COLS = 32;  // four rows at a time: few registers, three blocks an SM
 
 template <typename TC>
-__global__ void __launch_bounds__(FEW_WARPS * 32)
+__global__ void __launch_bounds__(FEW_WARPS * 32, 3)
 moe_fewrows_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W, TC* __restrict__ C,
                    const int32_t* __restrict__ offsets, const int32_t* __restrict__ row_pair, int N, int K, int top, int gather,
                    int act) {
@@ -366,33 +366,50 @@ moe_fewrows_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
       reinterpret_cast<uint4*>(rows)[i] = v;
     }
     __syncthreads();
-    for (int n = n0 + warp; n < min(N, n0 + FEW_COLS); n += FEW_WARPS) {
-      const uint4* wrow = reinterpret_cast<const uint4*>(We + (size_t)n * K);
-      float acc[FEW_ROWS];
+    // a warp's four columns side by side: their pieces of the weight rows are asked for together
+    constexpr int NC = FEW_COLS / FEW_WARPS;
+    const uint4* wrow[NC];
 #pragma unroll
-      for (int r = 0; r < FEW_ROWS; ++r) acc[r] = 0.f;
-      for (int c = lane; c < K / 8; c += 32) {
-        const uint4 wraw = wrow[c];
-        const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wraw);
-        float2 wf[4];
+    for (int j = 0; j < NC; ++j) wrow[j] = reinterpret_cast<const uint4*>(We + (size_t)min(N - 1, n0 + warp + j * FEW_WARPS) * K);
+    float acc[NC][FEW_ROWS];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) wf[j] = __bfloat1622float2(w2[j]);
+    for (int j = 0; j < NC; ++j)
 #pragma unroll
-        for (int r = 0; r < FEW_ROWS; ++r) {
-          const uint4 araw = reinterpret_cast<const uint4*>(rows + (size_t)r * K)[c];
-          const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&araw);
+      for (int r = 0; r < FEW_ROWS; ++r) acc[j][r] = 0.f;
+#pragma unroll 2
+    for (int c = lane; c < K / 8; c += 32) {
+      uint4 wraw[NC];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 af = __bfloat1622float2(a2[j]);
-            acc[r] = fmaf(af.x, wf[j].x, acc[r]);
-            acc[r] = fmaf(af.y, wf[j].y, acc[r]);
+      for (int j = 0; j < NC; ++j) wraw[j] = wrow[j][c];
+      float2 af[FEW_ROWS][4];
+#pragma unroll
+      for (int r = 0; r < FEW_ROWS; ++r) {
+        const uint4 araw = reinterpret_cast<const uint4*>(rows + (size_t)r * K)[c];
+        const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&araw);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) af[r][q] = __bfloat1622float2(a2[q]);
+      }
+#pragma unroll
+      for (int j = 0; j < NC; ++j) {
+        const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wraw[j]);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float2 wf = __bfloat1622float2(w2[q]);
+#pragma unroll
+          for (int r = 0; r < FEW_ROWS; ++r) {
+            acc[j][r] = fmaf(af[r][q].x, wf.x, acc[j][r]);
+            acc[j][r] = fmaf(af[r][q].y, wf.y, acc[j][r]);
           }
         }
       }
+    }
+#pragma unroll
+    for (int j = 0; j < NC; ++j) {
+      const int n = n0 + warp + j * FEW_WARPS;
 #pragma unroll
       for (int r = 0; r < FEW_ROWS; ++r) {
-        const float v = warp_sum(acc[r]);
-        if (lane == 0 && r < m) C[(size_t)(r0 + r) * N + n] = from_float<TC>(moe_act(v, act));
+        const float v = warp_sum(acc[j][r]);
+        if (lane == 0 && r < m && n < N) C[(size_t)(r0 + r) * N + n] = from_float<TC>(moe_act(v, act));
       }
     }
   }
@@ -470,7 +487,7 @@ PSB_API int psb_moe_gemm(const void* a, int a_dtype, const void* w, int w_dtype,
   const size_t few_smem = (size_t)FEW_ROWS * K * sizeof(__nv_bfloat16);
   if (a_dtype == PSB_BF16 && w_dtype == PSB_BF16 && K % 8 == 0 && (((uintptr_t)a | (uintptr_t)w) & 15) == 0 &&
       pairs <= FEW_ROWS * E && few_smem <= 192 * 1024 && E <= 65535) {
-    // no more rows than eight an expert on average: stream every used expert's matrix once
+    // no more rows than four an expert on average: stream every used expert's matrix once
     const dim3 few_grid((N + FEW_COLS - 1) / FEW_COLS, E);
     PSB_DISPATCH_DTYPE(c_dtype, TC, {
       auto kernel = moe_fewrows_kernel<TC>;

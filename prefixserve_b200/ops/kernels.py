@@ -752,6 +752,9 @@ def norm_add_norm(h: torch.Tensor, y: torch.Tensor, gain_post: torch.Tensor, eps
 
 BIASED_TILE_MIN_TOKENS = 16  # portions from this many tokens on go to the kernels that stage keys for a tile of tokens
 BIASED_MMA = True            # ... the tensor-core one where the sizes allow (multiples of 8 up to 128), else the CUDA-core one
+# The tensor-core kernel also takes single tokens and short portions: its blocks bring keys and values in with wide,
+# coalesced loads of all threads, which is what a decode step is bound by (the rows of its tile that have no token idle).
+BIASED_MMA_MIN_TOKENS = 1
 
 
 def biased_attention(qkv: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, ctx, *, num_heads: int, num_kv_heads: int,
@@ -786,25 +789,28 @@ def biased_attention(qkv: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, c
     # kernel a token gets depends on the length of its portion only (decided on the device from the item offsets, so
     # the launches have the same shape whatever the step holds).
     item_start = _i32(ctx.item_start, "item offsets")
-    long_portions = qkv.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16 and ctx.max_new_tokens >= BIASED_TILE_MIN_TOKENS
-    on_tensor_cores = long_portions and BIASED_MMA and bool(lib().psb_attention_biased_mma_supported(num_heads, num_kv_heads, dim, vdim))
+    both16 = qkv.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16
+    on_tensor_cores = both16 and BIASED_MMA and bool(lib().psb_attention_biased_mma_supported(num_heads, num_kv_heads, dim, vdim))
+    least = BIASED_MMA_MIN_TOKENS if on_tensor_cores else BIASED_TILE_MIN_TOKENS
+    long_portions = both16 and ctx.max_new_tokens >= least
     tiled = long_portions and (on_tensor_cores or bool(lib().psb_attention_biased_tile_supported(num_heads, num_kv_heads, dim, vdim)))
-    if not (tiled and ctx.num_items == 1):  # a step that is one long portion has nothing for the walking kernel
+    if not (tiled and (ctx.num_items == 1 or least <= 1)):  # nothing for the walking kernel when every portion is tiled
         check(lib().psb_attention_biased(q.data_ptr(), _code(q, "queries"), kv.data_ptr(), _code(kv, "cache entry"),
                                          table.data_ptr(), table.shape[1], positions.data_ptr(), token_item.data_ptr(),
                                          _ptr(bias), _ptr(sink), out.data_ptr(), t, num_heads, num_kv_heads, dim, vdim,
                                          page_size, win, chk, reach, float(scale), item_start.data_ptr(),
-                                         BIASED_TILE_MIN_TOKENS if tiled else 0, _stream()), "attention_biased")
+                                         least if tiled else 0, _stream()), "attention_biased")
     if tiled:
         entry = lib().psb_attention_biased_mma if on_tensor_cores else lib().psb_attention_biased_tiles
         check(entry(q.data_ptr(), kv.data_ptr(), table.data_ptr(), table.shape[1], positions.data_ptr(), item_start.data_ptr(),
-                    ctx.num_items, t, BIASED_TILE_MIN_TOKENS, _ptr(bias), _ptr(sink), out.data_ptr(), num_heads, num_kv_heads, dim,
+                    ctx.num_items, t, least, _ptr(bias), _ptr(sink), out.data_ptr(), num_heads, num_kv_heads, dim,
                     vdim, page_size, win, chk, reach, float(scale), _stream()),
               "attention_biased_mma" if on_tensor_cores else "attention_biased_tiles")
     return out
 
 
-DELTA_LONG_PORTION = 32  # steps whose longest portion has this many tokens take 16 lanes a column of the state, else 4
+DELTA_LONG_PORTION = 32  # steps whose longest portion has this many tokens take DELTA_LONG_LANES lanes a column of the state, else 4
+DELTA_LONG_LANES = 16   # measured: 32 lanes (a column a warp) took 807 us for a 2,048-token portion with 16 heads of 128 x 128, 16 lanes 716
 
 
 def delta_rule(proj: torch.Tensor, ba: torch.Tensor, taps: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
@@ -835,7 +841,7 @@ def delta_rule(proj: torch.Tensor, ba: torch.Tensor, taps: torch.Tensor, a_log: 
                                   item_start.data_ptr(), slots.data_ptr(), qkv.data_ptr(), bd.data_ptr(), t, groups, heads, dim, vdim,
                                   k, state.shape[0], slot_floats, _stream()), "delta_prepare")
     o = torch.empty((t, heads, vdim), dtype=torch.float32, device=dev)
-    lanes = 16 if ctx.max_new_tokens >= DELTA_LONG_PORTION and dim >= 32 else 4
+    lanes = DELTA_LONG_LANES if ctx.max_new_tokens >= DELTA_LONG_PORTION and dim >= DELTA_LONG_LANES else 4
     check(lib().psb_delta_rule(qkv.data_ptr(), bd.data_ptr(), proj.data_ptr(), _code(proj, "projection output"), state.data_ptr(),
                                item_start.data_ptr(), slots.data_ptr(), o.data_ptr(), ctx.num_items, groups, heads, dim, vdim, k,
                                state.shape[0], slot_floats, lanes, _stream()), "delta_rule")
