@@ -4,8 +4,9 @@
 //   h <- h + gain_post * y / sqrt(mean(y^2) + eps)            (float32 stream, updated in place)
 //   x  = gain_pre * h / sqrt(mean(h^2) + eps)                  (optional; in the compute type)
 //
-// One block per row; the new stream row stays in shared memory between the sum and the second norm, so the stream
-// is read once and written once and y is read twice (the second time from the cache).  With ``rows`` the second
+// One block per row.  Rows of up to 4,096 numbers live in registers from one read to the last write (the gains are
+// asked for ahead of the dependency wait); longer rows keep the new stream row in shared memory between the sum and
+// the second norm and read y twice (the second time from the cache).  With ``rows`` the second
 // norm is taken of the chosen rows only and written densely (the last use of the stream: the wanted positions);
 // the update of the stream is then left out for rows that are not chosen.  Statistics and sums are float32, every
 // thread adds the warps' partial sums in the same order.
@@ -56,6 +57,56 @@ norm_add_norm_kernel(float* __restrict__ h, const TY* __restrict__ y, const floa
   for (int j = threadIdx.x; j < H; j += blockDim.x) xr[j] = from_float<TX>(gain_pre[j] * (fresh[j] * inv_h));
 }
 
+// Rows of up to 256 * ITEMS numbers: everything a thread needs (its share of y, of the stream and of the two gains) is
+// asked for at once and kept in registers, so the row is read once and the kernel waits for memory once.
+template <typename TY, typename TX, int ITEMS>
+__global__ void __launch_bounds__(256)
+norm_add_norm_regs_kernel(float* __restrict__ h, const TY* __restrict__ y, const float* __restrict__ gain_post,
+                          const float* __restrict__ gain_pre, const int32_t* __restrict__ rows, TX* __restrict__ x, int H,
+                          float eps_post, float eps_pre) {
+  __shared__ float scratch[32];
+  pdl_trigger();
+  float gpost[ITEMS], gpre[ITEMS];
+#pragma unroll
+  for (int k = 0; k < ITEMS; ++k) {  // weights: before the wait
+    const int j = threadIdx.x + 256 * k;
+    gpost[k] = j < H ? gain_post[j] : 0.f;
+    gpre[k] = (gain_pre && j < H) ? gain_pre[j] : 0.f;
+  }
+  pdl_wait();
+  const int i = blockIdx.x;
+  const int r = rows ? rows[i] : i;
+  float* hr = h + (size_t)r * H;
+  const TY* yr = y + (size_t)r * H;
+  float yv[ITEMS], hv[ITEMS];
+#pragma unroll
+  for (int k = 0; k < ITEMS; ++k) {
+    const int j = threadIdx.x + 256 * k;
+    yv[k] = j < H ? to_float<TY>(yr[j]) : 0.f;
+    hv[k] = j < H ? hr[j] : 0.f;
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < ITEMS; ++k) ss = fmaf(yv[k], yv[k], ss);
+  const float inv_y = 1.f / sqrtf(block_total(ss, scratch) / (float)H + eps_post);
+  ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < ITEMS; ++k) {
+    const int j = threadIdx.x + 256 * k;
+    hv[k] = hv[k] + gpost[k] * (yv[k] * inv_y);
+    if (!rows && j < H) hr[j] = hv[k];
+    ss = fmaf(hv[k], hv[k], ss);  // beyond H: 0 + 0 * ...
+  }
+  if (!x) return;
+  const float inv_h = 1.f / sqrtf(block_total(ss, scratch) / (float)H + eps_pre);
+  TX* xr = x + (size_t)i * H;
+#pragma unroll
+  for (int k = 0; k < ITEMS; ++k) {
+    const int j = threadIdx.x + 256 * k;
+    if (j < H) xr[j] = from_float<TX>(gpre[k] * (hv[k] * inv_h));
+  }
+}
+
 }  // namespace
 
 // (h, y, y_dtype, gain_post, gain_pre, rows, x, x_dtype, n_rows, H, eps_post, eps_pre, stream)
@@ -69,8 +120,15 @@ PSB_API int psb_norm_add_norm(void* h, const void* y, int y_dtype, const void* g
   if (n_rows == 0) return 0;
   PSB_DISPATCH_DTYPE(y_dtype, TY, {
     PSB_DISPATCH_DTYPE(x_dtype, TX, {
-      psb_launch(norm_add_norm_kernel<TY, TX>, dim3(n_rows), dim3(256), smem, stream, (float*)h, (const TY*)y,
-                 (const float*)gain_post, (const float*)gain_pre, (const int32_t*)rows, (TX*)x, H, eps_post, eps_pre);
+      if (H <= 256 * 4)
+        psb_launch(norm_add_norm_regs_kernel<TY, TX, 4>, dim3(n_rows), dim3(256), 0, stream, (float*)h, (const TY*)y,
+                   (const float*)gain_post, (const float*)gain_pre, (const int32_t*)rows, (TX*)x, H, eps_post, eps_pre);
+      else if (H <= 256 * 16)
+        psb_launch(norm_add_norm_regs_kernel<TY, TX, 16>, dim3(n_rows), dim3(256), 0, stream, (float*)h, (const TY*)y,
+                   (const float*)gain_post, (const float*)gain_pre, (const int32_t*)rows, (TX*)x, H, eps_post, eps_pre);
+      else
+        psb_launch(norm_add_norm_kernel<TY, TX>, dim3(n_rows), dim3(256), smem, stream, (float*)h, (const TY*)y,
+                   (const float*)gain_post, (const float*)gain_pre, (const int32_t*)rows, (TX*)x, H, eps_post, eps_pre);
     });
   });
   PSB_LAUNCH_CHECK("norm_add_norm");

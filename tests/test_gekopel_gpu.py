@@ -264,12 +264,13 @@ def test_position_embedding_alone():
     assert torch.allclose(h.cpu(), table.bfloat16().float()[ids] * 16.0 + pos.bfloat16().float()[places], atol=1e-5)
 
 
+@pytest.mark.parametrize("width", [40, 1500, 5000])   # rows in few registers, in many, and through shared memory
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_both_norms_of_a_sublayer_boundary_alone(dtype):
+def test_both_norms_of_a_sublayer_boundary_alone(dtype, width):
     from prefixserve_b200 import ops
     g = torch.Generator().manual_seed(1)
-    h, y = torch.randn(7, 40, generator=g), (3 * torch.randn(7, 40, generator=g)).to(dtype)
-    post, pre = 1 + 0.1 * torch.randn(40, generator=g), 1 + 0.1 * torch.randn(40, generator=g)
+    h, y = torch.randn(7, width, generator=g), (3 * torch.randn(7, width, generator=g)).to(dtype)
+    post, pre = 1 + 0.1 * torch.randn(width, generator=g), 1 + 0.1 * torch.randn(width, generator=g)
     new = h.double() + plain.rms(y.double(), 3e-6) * post.double()
     want = plain.rms(new, 2e-5) * pre.double()
     hd = h.cuda()
