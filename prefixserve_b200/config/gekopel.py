@@ -25,7 +25,7 @@ from .llama import UnsupportedModelError
 from .nerenex import _need, _positive
 
 ARCHITECTURE = "Gekopel"
-DEFAULT_BIAS_ROWS = 32  # rows of a layer's distance-bias table when a configuration is made here (random-weights mode)
+DEFAULT_BIAS_ROWS = 64  # rows of a layer's distance-bias table when a configuration is made here (random-weights mode)
 
 
 @dataclass(frozen=True)

@@ -96,7 +96,7 @@ PRESETS.update({
             {"type": "delta", "mixer": {"heads": 4, "kv_heads": 2, "dim": 16, "vdim": 24, "conv": 4}, "mlp": {"kind": "dense", "ff": 128}},
             {"type": "attention", "mixer": {"heads": 4, "kv_heads": 2, "dim": 16, "vdim": 24, "scale": 0.25, "bias_max": 48, "mask": {"size": 40}},
              "mlp": {"kind": "moe", "expert": {"ff": 32}, "shared": {"ff": 48},
-                     "router": {"experts": 8, "top": 2, "scale": 1.5, "groups": {"count": 4, "keep": 2}}}},
+                     "router": {"experts": 8, "top": 2, "scale": 1.25, "groups": {"count": 4, "keep": 2}}}},
         ],
     },
     # layer sizes of a 1B- and an 8B-class decoder (width, heads), for the benchmarks: per token 4 of 32 experts and a shared one

@@ -79,7 +79,7 @@ def test_cache_needs_chunk_groups_and_states(tmp_path):
     assert [cache.free_pages(g) for g in range(3)] == [40, 40, 40]
 
 
-@pytest.mark.parametrize("rows, reach", [(32, 120), (10, 24), (11, 50), (6, 9), (32, 300), (16, 128), (2, 5)])
+@pytest.mark.parametrize("rows, reach", [(32, 100), (10, 24), (11, 50), (6, 9), (32, 300), (16, 128), (2, 5)])
 def test_distance_buckets(rows, reach):
     from prefixserve_b200.parts.biased_attention import distance_bucket
     half = rows // 2

@@ -260,8 +260,8 @@ def test_position_embedding_alone():
     ids, places = [4, 9, 9, 49, 0], [0, 1, 29, 7, 7]
     h = ops.embedding_positions(dev(ids), dev(places), table.cuda(), pos.cuda(), 2.5)
     assert torch.allclose(h.cpu(), table[ids] * 2.5 + pos[places], atol=1e-6)
-    h = ops.embedding_positions(dev(ids), dev(places), table.bfloat16().cuda(), pos.bfloat16().cuda(), 16.0)
-    assert torch.allclose(h.cpu(), table.bfloat16().float()[ids] * 16.0 + pos.bfloat16().float()[places], atol=1e-5)
+    h = ops.embedding_positions(dev(ids), dev(places), table.bfloat16().cuda(), pos.bfloat16().cuda(), 12.0)
+    assert torch.allclose(h.cpu(), table.bfloat16().float()[ids] * 12.0 + pos.bfloat16().float()[places], atol=1e-5)
 
 
 @pytest.mark.parametrize("width", [40, 1500, 5000])   # rows in few registers, in many, and through shared memory
@@ -288,7 +288,7 @@ def test_both_norms_of_a_sublayer_boundary_alone(dtype, width):
     assert torch.allclose(hd.cpu().double(), new, atol=1e-5)
 
 
-@pytest.mark.parametrize("experts, top, groups, keep", [(8, 4, 4, 3), (6, 2, 3, 1), (5, 1, 5, 2), (4, 4, 1, 1), (64, 6, 8, 4), (12, 12, 3, 3)])
+@pytest.mark.parametrize("experts, top, groups, keep", [(8, 3, 4, 2), (6, 2, 3, 1), (5, 1, 5, 2), (4, 4, 1, 1), (64, 6, 8, 4), (12, 12, 3, 3)])
 def test_router_alone(experts, top, groups, keep):
     from prefixserve_b200 import ops
     g = torch.Generator().manual_seed(experts)
