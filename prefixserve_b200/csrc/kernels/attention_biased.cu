@@ -369,7 +369,6 @@ attention_biased_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
   __shared__ __align__(16) __nv_bfloat16 ks[MMA_KEYS * KS];   // keys [key][d]; first the tile's queries [row][d]
   __shared__ __align__(16) __nv_bfloat16 vt[V * VS];          // values transposed [v][key]
   __shared__ float near_bias[MMA_BIAS];                       // the head's bias for the nearest distances
-  pdl_trigger();
   pdl_wait();
   int item = -1, t0 = 0;
   for (int i = 0, left = blockIdx.x; i < items; ++i) {
@@ -534,6 +533,7 @@ attention_biased_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
       }
     }
   }
+  pdl_trigger();  // late: blocks of the next kernel waiting beside this one's few warps would only be in their way
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);

@@ -47,7 +47,6 @@ delta_prepare_kernel(const T* __restrict__ proj, const float* __restrict__ ba, c
                      int T_tokens, int tokens_per_block) {
   extern __shared__ float row[];  // the unit's convolved, activated channels
   __shared__ float scratch[4];
-  pdl_trigger();
   const int unit = blockIdx.y;
   const int C = 2 * G * dim + H * vdim, P = C + H * vdim;
   const int c0 = unit < 2 * G ? unit * dim : 2 * G * dim + (unit - 2 * G) * vdim;
@@ -99,6 +98,10 @@ delta_prepare_kernel(const T* __restrict__ proj, const float* __restrict__ ba, c
     }
   }
   }
+  // At the end, not at the start: the recurrence behind this kernel has few blocks that live long.  Let in while this
+  // kernel's blocks fill the SMs, they crowd onto the few SMs with room and stay there, several to a scheduler; a
+  // 2,048-token portion then took 1.4 ms a layer instead of 0.7.
+  pdl_trigger();
 }
 
 constexpr int RULE_WARPS = 4;
@@ -133,7 +136,6 @@ delta_rule_kernel(const float* __restrict__ qkv, const float* __restrict__ bd, c
   constexpr int COLS = 32 / R;  // columns a warp holds
   constexpr int RP = R * PER, BC = RULE_WARPS * COLS, W = (2 * RP + BC + 2 + 3) / 4 * 4;
   static_assert(RP % 4 == 0, "queries and keys of a token start on 16 bytes");
-  pdl_trigger();
   const int C = 2 * G * dim + H * vdim, P = C + H * vdim;
   const int h = blockIdx.y, item = blockIdx.z;
   const int g = h / (H / G);
@@ -238,6 +240,9 @@ delta_rule_kernel(const float* __restrict__ qkv, const float* __restrict__ bd, c
       if (live && r == 0) o[((size_t)(ts + i) * H + h) * vdim + col] = fmaf(qk, u, dec * qsum);
     }
   }
+  // Only now may the next kernel's blocks come: this kernel has two warps a scheduler and is bound by their chains of
+  // dependent instructions, and the next kernel reads what the last token writes anyway.
+  pdl_trigger();
 #pragma unroll
   for (int e = 0; e < PER; ++e) {
     const int d = r * PER + e;
