@@ -22,6 +22,8 @@
 // per request also brings the slot's convolution inputs up to date (the last K-1 rows of the projection, or what
 // was there before, moved up, when the portion is shorter).
 //
+// delta_cross_kernel (a warp per token and head): q.k, and k.k' and q.k' with the key of the token before.
+//
 // delta_finish_kernel (a warp per token and head): o / sqrt(mean(o^2) + eps) * gain[vdim] * silu(gate), rounded to
 // the compute type for the output projection.
 //
@@ -31,6 +33,9 @@
 namespace {
 
 constexpr int MAX_TAPS = 16;
+// Per token and head the recurrence is handed five numbers, [T, BD, H]: beta, decay, and three dot products that do
+// not depend on the state: q.k of the token, and k.k' and q.k' with the key k' of the token before it in the portion.
+constexpr int BD = 5;
 
 __device__ __forceinline__ float softplusf_(float x) { return log1pf(expf(-fabsf(x))) + fmaxf(x, 0.f); }
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-x)); }
@@ -93,8 +98,8 @@ delta_prepare_kernel(const T* __restrict__ proj, const float* __restrict__ ba, c
   for (int i = threadIdx.x; i < len; i += blockDim.x) out[i] = row[i] * factor;  // a thread reads back what it wrote
   if (unit == 0) {
     for (int h = threadIdx.x; h < H; h += blockDim.x) {
-      bd[(size_t)t * 2 * H + h] = sigmoidf_(ba[(size_t)t * 2 * H + h]);
-      bd[(size_t)t * 2 * H + H + h] = expf(-expf(a_log[h]) * softplusf_(ba[(size_t)t * 2 * H + H + h] + dt_bias[h]));
+      bd[(size_t)t * BD * H + h] = sigmoidf_(ba[(size_t)t * 2 * H + h]);
+      bd[(size_t)t * BD * H + H + h] = expf(-expf(a_log[h]) * softplusf_(ba[(size_t)t * 2 * H + H + h] + dt_bias[h]));
     }
   }
   }
@@ -102,6 +107,37 @@ delta_prepare_kernel(const T* __restrict__ proj, const float* __restrict__ ba, c
   // kernel's blocks fill the SMs, they crowd onto the few SMs with room and stay there, several to a scheduler; a
   // 2,048-token portion then took 1.4 ms a layer instead of 0.7.
   pdl_trigger();
+}
+
+// A warp per (token, head): the three state-free dot products of the unit vectors delta_prepare_kernel left.
+__global__ void __launch_bounds__(128)
+delta_cross_kernel(const float* __restrict__ qkv, const int32_t* __restrict__ token_item, const int32_t* __restrict__ item_start,
+                   float* __restrict__ bd, long long units, int G, int H, int dim, int vdim) {
+  pdl_wait();  // (no early trigger: the recurrence comes next, see the end of delta_prepare_kernel)
+  const long long unit = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (unit >= units) return;
+  const long long t = unit / H;
+  const int h = (int)(unit - t * H), g = h / (H / G);
+  const int C = 2 * G * dim + H * vdim;
+  const float* q = qkv + (size_t)t * C + (size_t)g * dim;
+  const float* k = q + (size_t)G * dim;
+  const bool first = t == item_start[token_item[t]];  // no token before it in this step's portion
+  const float* kp = first ? k : k - C;
+  float qk = 0.f, kk = 0.f, qkp = 0.f;
+  for (int d = lane; d < dim; d += 32) {
+    const float qv = q[d], kv = k[d], pv = kp[d];
+    qk = fmaf(qv, kv, qk);
+    kk = fmaf(kv, pv, kk);
+    qkp = fmaf(qv, pv, qkp);
+  }
+  qk = warp_sum(qk); kk = warp_sum(kk); qkp = warp_sum(qkp);
+  if (lane == 0) {
+    float* out = bd + (size_t)t * BD * H + h;
+    out[2 * H] = qk;
+    out[3 * H] = first ? 0.f : kk;
+    out[4 * H] = first ? 0.f : qkp;
+  }
 }
 
 constexpr int RULE_WARPS = 4;
@@ -122,10 +158,11 @@ __device__ __forceinline__ void copy_async_wait() {
 // (queries, keys, the block's value columns, beta, decay) is copied into shared memory one stage ahead of the
 // arithmetic (cp.async into the other of two buffers), so the chain from token to token never waits for memory.
 //
-// The chain itself is kept short: with S the state before the token, the three sums k.S, q.S (per column) and q.k are
-// finished by one butterfly, and then
+// The chain itself is kept short: with S the state before the token, the sums k.S and q.S (per column) are finished by
+// one butterfly, q.k comes ready-made (it does not depend on the state: delta_cross_kernel), and then
 //     u = beta (v - dec k.S),   o = dec q.S + (q.k) u,   S <- dec S + k u^T,
-// which is the read-out of the updated state written so that it does not wait for the update.
+// which is the read-out of the updated state written so that it does not wait for the update.  Tokens go two a round
+// (see the loop): one butterfly for both.
 template <typename T, int PER, int R>
 __global__ void __launch_bounds__(RULE_WARPS * 32)
 delta_rule_kernel(const float* __restrict__ qkv, const float* __restrict__ bd, const T* __restrict__ proj,
@@ -134,7 +171,7 @@ delta_rule_kernel(const float* __restrict__ qkv, const float* __restrict__ bd, c
                   int stage_tokens) {
   extern __shared__ __align__(16) float staged[];  // [2][stage_tokens][W]
   constexpr int COLS = 32 / R;  // columns a warp holds
-  constexpr int RP = R * PER, BC = RULE_WARPS * COLS, W = (2 * RP + BC + 2 + 3) / 4 * 4;
+  constexpr int RP = R * PER, BC = RULE_WARPS * COLS, W = (2 * RP + BC + BD + 3) / 4 * 4;
   static_assert(RP % 4 == 0, "queries and keys of a token start on 16 bytes");
   const int C = 2 * G * dim + H * vdim, P = C + H * vdim;
   const int h = blockIdx.y, item = blockIdx.z;
@@ -172,10 +209,10 @@ delta_rule_kernel(const float* __restrict__ qkv, const float* __restrict__ bd, c
         else buf[tok * W + e] = 0.f;
       }
     }
-    for (int i = threadIdx.x; i < n * (BC + 2); i += blockDim.x) {
-      const int tok = i / (BC + 2), e = i - tok * (BC + 2);
+    for (int i = threadIdx.x; i < n * (BC + BD); i += blockDim.x) {
+      const int tok = i / (BC + BD), e = i - tok * (BC + BD);
       float* dst = buf + tok * W + 2 * RP + e;
-      if (e >= BC) copy_async4(dst, bd + (size_t)(ts + tok) * 2 * H + (e - BC) * H + h);
+      if (e >= BC) copy_async4(dst, bd + (size_t)(ts + tok) * BD * H + (e - BC) * H + h);
       else if (col0 + e < vdim) copy_async4(dst, qkv + (size_t)(ts + tok) * C + 2 * G * dim + h * vdim + col0 + e);
       else *dst = 0.f;
     }
@@ -195,9 +232,7 @@ delta_rule_kernel(const float* __restrict__ qkv, const float* __restrict__ bd, c
     __syncthreads();  // this stage has landed for everybody, and everybody has left the other buffer
     if (ts + stage_tokens < t1) stage(ts + stage_tokens, staged + (size_t)(which_buf ^ 1) * stage_tokens * W);
     const float* buf = staged + (size_t)which_buf * stage_tokens * W;
-    for (int i = 0; i < n; ++i) {
-      const float* tokrow = buf + i * W;
-      float qq[PER], kk[PER];
+    auto load_qk = [&](const float* tokrow, float (&qq)[PER], float (&kk)[PER]) {
       if constexpr (PER % 4 == 0) {
 #pragma unroll
         for (int e = 0; e < PER; e += 4) {
@@ -213,18 +248,63 @@ delta_rule_kernel(const float* __restrict__ qkv, const float* __restrict__ bd, c
           kk[e] = tokrow[RP + r * PER + e];
         }
       }
+    };
+    int i = 0;
+    // Two tokens a round.  With S the state before token a and b = a + 1, the four sums k_a.S, q_a.S, k_b.S, q_b.S are
+    // finished by one butterfly; what token b needs of token a's write comes through the state-free products:
+    //   u_a = beta_a (v_a - dec_a k_a.S),                              o_a = dec_a q_a.S + (q_a.k_a) u_a,
+    //   u_b = beta_b (v_b - dec_b (dec_a k_b.S + (k_a.k_b) u_a)),      o_b = dec_b (dec_a q_b.S + (q_b.k_a) u_a) + (q_b.k_b) u_b,
+    //   S <- dec_b dec_a S + k_a (dec_b u_a)^T + k_b u_b^T.
+    for (; i + 1 < n; i += 2) {
+      const float* ra = buf + i * W;
+      const float* rb = ra + W;
+      float qa[PER], ka[PER], qb[PER], kb[PER];
+      load_qk(ra, qa, ka);
+      load_qk(rb, qb, kb);
+      const float va = ra[2 * RP + in_block], vb = rb[2 * RP + in_block];
+      const float beta_a = ra[2 * RP + BC], dec_a = ra[2 * RP + BC + 1], qk_a = ra[2 * RP + BC + 2];
+      const float beta_b = rb[2 * RP + BC], dec_b = rb[2 * RP + BC + 1], qk_b = rb[2 * RP + BC + 2];
+      const float kk_ab = rb[2 * RP + BC + 3], qk_ba = rb[2 * RP + BC + 4];
+      float kas = 0.f, qas = 0.f, kbs = 0.f, qbs = 0.f;
+#pragma unroll
+      for (int e = 0; e < PER; ++e) {
+        kas = fmaf(ka[e], s[e], kas);
+        qas = fmaf(qa[e], s[e], qas);
+        kbs = fmaf(kb[e], s[e], kbs);
+        qbs = fmaf(qb[e], s[e], qbs);
+      }
+#pragma unroll
+      for (int off = 1; off < R; off <<= 1) {
+        kas += __shfl_xor_sync(0xffffffffu, kas, off);
+        qas += __shfl_xor_sync(0xffffffffu, qas, off);
+        kbs += __shfl_xor_sync(0xffffffffu, kbs, off);
+        qbs += __shfl_xor_sync(0xffffffffu, qbs, off);
+      }
+      const float ua = beta_a * (va - dec_a * kas);
+      const float ub = beta_b * (vb - dec_b * fmaf(kk_ab, ua, dec_a * kbs));
+      const float dd = dec_b * dec_a, wa = dec_b * ua;
+#pragma unroll
+      for (int e = 0; e < PER; ++e) s[e] = fmaf(kb[e], ub, fmaf(ka[e], wa, dd * s[e]));
+      if (live && r == 0) {
+        float* orow = o + ((size_t)(ts + i) * H + h) * vdim + col;
+        orow[0] = fmaf(qk_a, ua, dec_a * qas);
+        orow[(size_t)H * vdim] = fmaf(qk_b, ub, dec_b * fmaf(qk_ba, ua, dec_a * qbs));
+      }
+    }
+    for (; i < n; ++i) {  // a portion's last token when their number is odd (a single decoded token)
+      const float* tokrow = buf + i * W;
+      float qq[PER], kk[PER];
+      load_qk(tokrow, qq, kk);
       const float v = tokrow[2 * RP + in_block];
-      const float beta = tokrow[2 * RP + BC], dec = tokrow[2 * RP + BC + 1];
-      float ks0 = 0.f, ks1 = 0.f, qs0 = 0.f, qs1 = 0.f, qk = 0.f;
+      const float beta = tokrow[2 * RP + BC], dec = tokrow[2 * RP + BC + 1], qk = tokrow[2 * RP + BC + 2];
+      float ks0 = 0.f, ks1 = 0.f, qs0 = 0.f, qs1 = 0.f;
 #pragma unroll
       for (int e = 0; e < PER; e += 2) {
         ks0 = fmaf(kk[e], s[e], ks0);
         qs0 = fmaf(qq[e], s[e], qs0);
-        qk = fmaf(qq[e], kk[e], qk);
         if (e + 1 < PER) {
           ks1 = fmaf(kk[e + 1], s[e + 1], ks1);
           qs1 = fmaf(qq[e + 1], s[e + 1], qs1);
-          qk = fmaf(qq[e + 1], kk[e + 1], qk);
         }
       }
       float ksum = ks0 + ks1, qsum = qs0 + qs1;
@@ -232,7 +312,6 @@ delta_rule_kernel(const float* __restrict__ qkv, const float* __restrict__ bd, c
       for (int off = 1; off < R; off <<= 1) {
         ksum += __shfl_xor_sync(0xffffffffu, ksum, off);
         qsum += __shfl_xor_sync(0xffffffffu, qsum, off);
-        qk += __shfl_xor_sync(0xffffffffu, qk, off);
       }
       const float u = beta * (v - dec * ksum);
 #pragma unroll
@@ -294,7 +373,7 @@ template <typename T, int PER, int R>
 void launch_rule(dim3 grid, cudaStream_t stream, const float* qkv, const float* bd, const T* proj, float* state,
                  const int32_t* item_start, const int32_t* slots, float* o, int G, int H, int dim, int vdim, int K,
                  int num_slots, size_t slot_floats) {
-  constexpr int W = (2 * R * PER + RULE_WARPS * (32 / R) + 2 + 3) / 4 * 4;
+  constexpr int W = (2 * R * PER + RULE_WARPS * (32 / R) + BD + 3) / 4 * 4;
   // two buffers within the 48 KB a kernel has without asking: 16 tokens a stage for keys up to 128 numbers, 4 beyond
   const int stage_tokens = 2 * 16 * W * (int)sizeof(float) <= 48 * 1024 ? 16 : 4;
   static_assert(2 * 4 * W * sizeof(float) <= 48 * 1024, "a stage of four tokens fits the default shared memory twice");
@@ -327,6 +406,10 @@ PSB_API int psb_delta_prepare(const void* proj, int dtype, const void* ba, const
                (float*)qkv, (float*)bd, G, H, dim, vdim, K, num_slots, (size_t)slot_floats, T, per_block);
   });
   PSB_LAUNCH_CHECK("delta_prepare");
+  const long long units = (long long)T * H;
+  psb_launch(delta_cross_kernel, dim3((unsigned)((units + 3) / 4)), dim3(128), 0, stream, (const float*)qkv, (const int32_t*)token_item,
+             (const int32_t*)item_start, (float*)bd, units, G, H, dim, vdim);
+  PSB_LAUNCH_CHECK("delta_cross");
   return 0;
 }
 

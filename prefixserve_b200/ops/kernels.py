@@ -833,7 +833,7 @@ def delta_rule(proj: torch.Tensor, ba: torch.Tensor, taps: torch.Tensor, a_log: 
             raise KernelError(f"delta rule: {what} must be float32 with {n} numbers on the device")
     dev = proj.device
     qkv = torch.empty((t, c), dtype=torch.float32, device=dev)
-    bd = torch.empty((t, 2 * heads), dtype=torch.float32, device=dev)
+    bd = torch.empty((t, 5 * heads), dtype=torch.float32, device=dev)   # beta, decay and three state-free dot products per head
     positions, token_item = _i32(ctx.positions, "positions"), _i32(ctx.token_item, "token-to-item map")
     item_start, slots = _i32(ctx.item_start, "item offsets"), _i32(ctx.slots, "slots")
     check(lib().psb_delta_prepare(proj.data_ptr(), _code(proj, "projection output"), ba.data_ptr(), taps.data_ptr(), a_log.data_ptr(),
